@@ -1,0 +1,526 @@
+// FP8 (e4m3) block-scaled grouped GEMM for sm_100a: tcgen05.mma + TMEM + TMA.
+//
+// Replaces the reference's sm_90 CUTLASS grouped GEMM (src/gemm/aok_grouped_gemm/
+// src/operations/hopper_grouped_gemm_kernel.h:228-400) and, through its epilogues,
+// silu_activate (src/executor/activations.cu:9-40) and the weight multiply of
+// localReduce (src/scheduler/local_reducer.cu:137).
+//
+// Shape of the kernel
+//   * persistent: one CTA per SM walks tiles t = blockIdx.x, += gridDim.x of a
+//     ragged tile list built on the device from the expert prefix sum;
+//   * tile = 128 rows (tokens) x 256 weight rows, K step 128 (= one 128-byte
+//     swizzle atom of e4m3, four tcgen05.mma of K=32);
+//   * warp 0 issues TMA loads into a 4-stage shared-memory ring, warp 1 issues
+//     the MMAs into one of two 256-column TMEM buffers, warps 4..11 (two
+//     warpgroups) drain a TMEM buffer per K step with tcgen05.ld and fold it
+//     into fp32 register accumulators multiplied by a_scale[row,kb]*b_scale[nb,kb]
+//     (the scales are plain fp32, so the hardware's power-of-two block scaling
+//     cannot be used and the promotion is done on the CUDA cores);
+//   * every wait on an mbarrier is bounded: after ~2 s it records a code in the
+//     caller's status words, raises a CTA-wide abort flag, and every role leaves
+//     its loop, waits for copies in flight, frees TMEM and returns.
+//   * no TMA multicast is used anywhere.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace epsb {
+
+namespace {
+
+constexpr int kBM = 128;           // rows per tile
+constexpr int kBN = 256;           // weight rows per tile (two 128-row TMA boxes)
+constexpr int kBK = 128;           // K step (bytes == elements for e4m3)
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK;         // 16 KB
+constexpr int kBBytes = kBN * kBK;         // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 384;              // warpgroup 0: producers; warpgroups 1,2: epilogue
+constexpr int kTmemCols = 512;             // two accumulator buffers of 256 fp32 columns
+constexpr int kMaxExperts = 1024;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// tcgen05 instruction descriptor, kind::f8f6f4: D=f32 (bits 4-5 = 1), A=B=e4m3 (0), both K-major,
+// N>>3 at bits 17-22, M>>4 at bits 24-28.
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+// Shared-memory matrix descriptor, high word: stride-byte-offset 1024 B (8 rows x 128 B) >> 4 = 64,
+// descriptor version 1 (bits 46-47), layout SWIZZLE_128B = 2 (bits 61-63).
+constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+
+struct SharedStorage {
+  // tile ring first: every stage base must be 1024-byte aligned for the 128-byte swizzle
+  uint8_t tiles[kStages][kStageBytes];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t amax_bar;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  float amax_x[2][2][kBM];  // [tile parity][column half][row]
+  int32_t tile_prefix[kMaxExperts + 1];  // m-tiles before each expert
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, SharedStorage* sm, int32_t* status, int code) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (sm->abort_flag) return false;
+    if ((++spins & 0x3ff) == 0) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        sm->abort_flag = 1;
+        if (status != nullptr) {
+          atomicCAS(status, 0, code);
+          atomicExch(status + 1, (int)blockIdx.x);
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmParams {
+  const float* a_s;
+  const float* b_s;
+  const int32_t* excl;
+  void* C;
+  float* c_s;
+  const float* row_w;
+  int32_t* status;
+  int num_experts;
+  int64_t max_rows;
+  int64_t N;   // weight rows per expert (2I in gate/up mode)
+  int64_t K;
+  int n_tiles; // tiles along N per m-tile
+};
+
+struct TileCoord {
+  int e, row0, rows_left, n;  // expert, first GEMM row of the tile, valid rows from row0, n-tile index
+};
+
+__device__ __forceinline__ TileCoord locate_tile(int t, const GemmParams& p, const SharedStorage* sm) {
+  const int g = t / p.n_tiles;
+  TileCoord c;
+  c.n = t - g * p.n_tiles;
+  int lo = 0, hi = p.num_experts;  // find e with prefix[e] <= g < prefix[e+1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sm->tile_prefix[mid] <= g) lo = mid;
+    else hi = mid;
+  }
+  c.e = lo;
+  const int m = g - sm->tile_prefix[lo];
+  const int b = __ldg(p.excl + lo), e_ = __ldg(p.excl + lo + 1);
+  c.row0 = b + m * kBM;
+  c.rows_left = e_ - c.row0;
+  return c;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  SharedStorage* sm = reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = (int)(p.K / kBK);
+
+  // ---- set-up: barriers, TMEM, tile list
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&sm->tmem_full[b], 1);
+      mbar_init(&sm->tmem_empty[b], 8);  // one arrival per epilogue warp
+    }
+    mbar_init(&sm->amax_bar, 256);
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp == 2) {
+    // m-tiles before each expert: warp-wide scan, 32 experts per step
+    int carry = 0;
+    for (int e0 = 0; e0 < p.num_experts; e0 += 32) {
+      const int e = e0 + lane;
+      int mt = 0;
+      if (e < p.num_experts) mt = (__ldg(p.excl + e + 1) - __ldg(p.excl + e) + kBM - 1) / kBM;
+      int inc = mt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += n;
+      }
+      if (e < p.num_experts) sm->tile_prefix[e] = carry + inc - mt;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) sm->tile_prefix[p.num_experts] = carry;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  const int total_tiles = sm->tile_prefix[p.num_experts] * p.n_tiles;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------ TMA producer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = locate_tile(t, p, sm);
+        int brow0, brow1;  // first weight row of each 128-row box
+        if (kMode == EPSB_GEMM_GATEUP) {
+          brow0 = (int)(c.e * p.N + c.n * 128);
+          brow1 = (int)(c.e * p.N + p.N / 2 + c.n * 128);
+        } else {
+          brow0 = (int)(c.e * p.N + c.n * kBN);
+          brow1 = brow0 + 128;
+        }
+        for (int kb = 0; kb < KB; kb++, it++) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!(ok = mbar_wait(&sm->empty[s], ph ^ 1, sm, p.status, 11))) break;
+          mbar_expect_tx(&sm->full[s], kStageBytes);
+          uint8_t* base = sm->tiles[s];
+          tma_load_2d(base, &tmap_a, kb * kBK, c.row0, &sm->full[s]);
+          tma_load_2d(base + kABytes, &tmap_b, kb * kBK, brow0, &sm->full[s]);
+          tma_load_2d(base + kABytes + kABytes, &tmap_b, kb * kBK, brow1, &sm->full[s]);
+        }
+      }
+      if (!ok) {
+        // let copies already issued land before the CTA's shared memory is released
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------ MMA issuer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < KB; kb++, it++) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          const int buf = it & 1;
+          const uint32_t tph = (it >> 1) & 1;
+          if (!(ok = mbar_wait(&sm->tmem_empty[buf], tph ^ 1, sm, p.status, 21))) break;
+          if (!(ok = mbar_wait(&sm->full[s], ph, sm, p.status, 22))) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sm->tiles[s]);
+          const uint64_t da = ((uint64_t)kDescHi << 32) | (uint64_t)(((a_addr >> 4) & 0x3fffu) | (1u << 16));
+          const uint64_t db = ((uint64_t)kDescHi << 32) | (uint64_t)((((a_addr + kABytes) >> 4) & 0x3fffu) | (1u << 16));
+          const uint32_t d = tmem_base + (uint32_t)buf * kBN;
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; k4++) umma_f8(d, da + 2 * k4, db + 2 * k4, k4 > 0 ? 1u : 0u);
+          umma_commit(&sm->empty[s]);       // stage reusable once these MMAs have read it
+          umma_commit(&sm->tmem_full[buf]); // accumulator buffer ready for the epilogue
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ------------------------------------------------ epilogue: 8 warps
+    const int ew = warp - 4;           // 0..7
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may read
+    const int half = ew >> 2;          // which half of the tile's columns
+    const int r_in_tile = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int KBs = KB;                // scales per row
+    const int NB = (int)(p.N / 128);
+    uint32_t it = 0, amax_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord c = locate_tile(t, p, sm);
+      const int64_t grow = (int64_t)c.row0 + r_in_tile;
+      const bool row_ok = r_in_tile < c.rows_left;
+      const float* as_row = p.a_s + (row_ok ? grow : (int64_t)c.row0) * KBs;
+      // the two 128-wide scale blocks this thread's columns belong to
+      const float* bs0;
+      const float* bs1;
+      if (kMode == EPSB_GEMM_GATEUP) {
+        bs0 = p.b_s + ((int64_t)c.e * NB + c.n) * KBs;               // gate block
+        bs1 = p.b_s + ((int64_t)c.e * NB + NB / 2 + c.n) * KBs;      // up block
+      } else {
+        bs0 = p.b_s + ((int64_t)c.e * NB + min(c.n * 2 + half, NB - 1)) * KBs;
+        bs1 = bs0;
+      }
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; i++) acc[i] = 0.0f;
+      float sa = __ldg(as_row), sb0 = __ldg(bs0), sb1 = __ldg(bs1);
+      for (int kb = 0; kb < KB; kb++, it++) {
+        const int buf = it & 1;
+        const uint32_t tph = (it >> 1) & 1;
+        const float s0 = sa * sb0, s1 = sa * sb1;
+        if (kb + 1 < KB) {
+          sa = __ldg(as_row + kb + 1);
+          sb0 = __ldg(bs0 + kb + 1);
+          sb1 = __ldg(bs1 + kb + 1);
+        }
+        ok = mbar_wait(&sm->tmem_full[buf], tph, sm, p.status, 31);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tb = lane_addr + (uint32_t)buf * kBN;
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+          // gate/up mode: chunks 0,1 = gate columns [64*half, +64), chunks 2,3 = up columns [128+64*half, +64)
+          int col;
+          if (kMode == EPSB_GEMM_GATEUP) col = (ch < 2 ? 0 : 128) + 64 * half + (ch & 1) * 32;
+          else col = 128 * half + ch * 32;
+          float v[32];
+          tmem_ld32(tb + col, v);
+          const float s = (kMode == EPSB_GEMM_GATEUP && ch >= 2) ? s1 : s0;
+#pragma unroll
+          for (int i = 0; i < 32; i++) acc[ch * 32 + i] = fmaf(v[i], s, acc[ch * 32 + i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->tmem_empty[buf]);
+      }
+      if (!ok) break;
+
+      // ---- tile epilogue
+      if (kMode == EPSB_GEMM_GATEUP) {
+        const int64_t I = p.N / 2;
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 64; i++) {
+          const float g = acc[i], u = acc[64 + i];
+          const float a = (g / (1.0f + __expf(-g))) * u;
+          acc[i] = a;
+          amax = fmaxf(amax, fabsf(a));
+        }
+        sm->amax_x[amax_phase][half][r_in_tile] = amax;
+        mbar_arrive(&sm->amax_bar);
+        ok = mbar_wait(&sm->amax_bar, amax_phase, sm, p.status, 41);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        amax = fmaxf(amax, sm->amax_x[amax_phase][half ^ 1][r_in_tile]);
+        amax_phase ^= 1;
+        const float scale = __fdiv_rn(amax, kFp8Max);
+        const float inv = __frcp_rn(scale);
+        if (row_ok) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + grow * I + (int64_t)c.n * 128 + 64 * half;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int i = q4 * 16 + j * 4;
+              w[j] = (uint32_t)cvt_e4m3x2(quant_clamp(acc[i], inv), quant_clamp(acc[i + 1], inv)) |
+                     ((uint32_t)cvt_e4m3x2(quant_clamp(acc[i + 2], inv), quant_clamp(acc[i + 3], inv)) << 16);
+            }
+            st_16(dst + q4 * 16, make_uint4(w[0], w[1], w[2], w[3]));
+          }
+          if (half == 0) p.c_s[grow * (I / 128) + c.n] = scale;
+        }
+        // amax_x alternates between two copies: a copy is rewritten two tiles later, and a thread
+        // cannot pass the next tile's amax_bar before its partner has arrived there, i.e. has read.
+      } else {
+        const int64_t col0 = (int64_t)c.n * kBN + 128 * half;
+        if (row_ok && col0 < p.N) {
+          float wgt = 1.0f;
+          if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr) wgt = __ldg(p.row_w + grow);
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + (grow * p.N + col0) * 2;
+#pragma unroll
+          for (int q8 = 0; q8 < 16; q8++) {
+            uint4 o;
+            o.x = pack_bf16x2(acc[q8 * 8 + 0] * wgt, acc[q8 * 8 + 1] * wgt);
+            o.y = pack_bf16x2(acc[q8 * 8 + 2] * wgt, acc[q8 * 8 + 3] * wgt);
+            o.z = pack_bf16x2(acc[q8 * 8 + 4] * wgt, acc[q8 * 8 + 5] * wgt);
+            o.w = pack_bf16x2(acc[q8 * 8 + 6] * wgt, acc[q8 * 8 + 7] * wgt);
+            st_16(dst + q8 * 16, o);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D e4m3 tensor [rows, K] (K contiguous), box 128 x 128, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return fail(EPSB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, 128u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EPSB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return EPSB_OK;
+}
+
+template <int kMode>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  const size_t smem = sizeof(SharedStorage) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return fail(EPSB_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  grouped_gemm_fp8_kernel<kMode><<<grid, kThreads, smem, st>>>(ta, tb, p);
+  return check_launch("grouped_gemm_fp8");
+}
+
+}  // namespace
+
+}  // namespace epsb
+
+using namespace epsb;
+
+extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
+                                     const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K,
+                                     void* C, float* c_s, const float* row_w, int32_t* status, void* stream) {
+  EPSB_REQUIRE(mode == EPSB_GEMM_PLAIN || mode == EPSB_GEMM_GATEUP || mode == EPSB_GEMM_DOWN, EPSB_ERR_INVALID,
+               "unknown GEMM mode %d", mode);
+  EPSB_REQUIRE(num_experts > 0 && num_experts <= kMaxExperts, EPSB_ERR_INVALID, "num_experts %d out of range",
+               num_experts);
+  EPSB_REQUIRE(K > 0 && K % 128 == 0, EPSB_ERR_INVALID, "K: %lld is not divisible by 128", (long long)K);
+  EPSB_REQUIRE(N > 0 && N % 128 == 0, EPSB_ERR_INVALID, "N: %lld is not divisible by 128", (long long)N);
+  EPSB_REQUIRE(mode != EPSB_GEMM_GATEUP || (N % 256 == 0 && c_s != nullptr), EPSB_ERR_INVALID,
+               "gate/up mode needs N = 2*I with I %% 128 == 0 and an output scale buffer");
+  EPSB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)C & 15) == 0, EPSB_ERR_INVALID,
+               "A, B and C must be 16-byte aligned");
+  EPSB_REQUIRE((int64_t)num_experts * N < (1ll << 31) && max_rows < (1ll << 31), EPSB_ERR_INVALID,
+               "tensor too large for 32-bit TMA coordinates");
+  if (max_rows <= 0) return EPSB_OK;
+  CUtensorMap ta, tb;
+  int rc = make_map(&ta, A, max_rows, K);
+  if (rc) return rc;
+  rc = make_map(&tb, B, (int64_t)num_experts * N, K);
+  if (rc) return rc;
+  GemmParams p;
+  p.a_s = a_s;
+  p.b_s = b_s;
+  p.excl = excl;
+  p.C = C;
+  p.c_s = c_s;
+  p.row_w = row_w;
+  p.status = status;
+  p.num_experts = num_experts;
+  p.max_rows = max_rows;
+  p.N = N;
+  p.K = K;
+  p.n_tiles = mode == EPSB_GEMM_GATEUP ? (int)(N / 256) : (int)((N + kBN - 1) / kBN);
+  // tile-count upper bound without reading the device-side prefix sum
+  const int64_t m_tiles_max = (max_rows + kBM - 1) / kBM + num_experts;
+  int64_t grid = m_tiles_max * p.n_tiles;
+  if (grid > sm_count()) grid = sm_count();
+  auto st = static_cast<cudaStream_t>(stream);
+  switch (mode) {
+    case EPSB_GEMM_GATEUP: return launch<EPSB_GEMM_GATEUP>(ta, tb, p, (int)grid, st);
+    case EPSB_GEMM_DOWN: return launch<EPSB_GEMM_DOWN>(ta, tb, p, (int)grid, st);
+    default: return launch<EPSB_GEMM_PLAIN>(ta, tb, p, (int)grid, st);
+  }
+}

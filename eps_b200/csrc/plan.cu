@@ -1,0 +1,488 @@
+// Index plans of the EPS scheduler and of fast_ep, for sm_100a.
+//
+// Every plan of the reference is a stable counting sort whose visiting order is
+// an artefact of a strided single-CTA thread decomposition.  Here each plan is
+// one CTA of 32 warps running the same primitive: the positions are put in the
+// reference's visiting order ("virtual order"), cut into one contiguous range
+// per warp, counted per warp with warp-match votes (no atomics), scanned over
+// warps and over buckets, and emitted by rank.  The outputs are bit-identical
+// to the reference's for any input whose top-k ids are distinct per token.
+#include "common.cuh"
+
+namespace epsb {
+
+namespace {
+
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanWarps = kPlanThreads / 32;
+constexpr int kMaxBuckets = 1024;
+
+struct SortScratch {
+  int32_t* rows;   // [kPlanWarps][B] per-warp counts, then per-warp exclusive offsets
+  int32_t* base;   // [B] exclusive scan of the bucket totals
+  int32_t* total;  // [B]
+  int32_t* wsum;   // [kPlanWarps + 1]
+};
+
+__device__ __forceinline__ SortScratch carve(int32_t* smem, int B) {
+  SortScratch s;
+  s.rows = smem;
+  s.base = smem + kPlanWarps * B;
+  s.total = s.base + B;
+  s.wsum = s.total + B;
+  return s;
+}
+
+size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)(kPlanWarps + 2) * B + kPlanWarps + 1); }
+
+// Inclusive scan of one value per thread over the whole 1024-thread CTA.
+__device__ __forceinline__ int block_inclusive_scan(int v, int32_t* wsum) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, v, off);
+    if (lane >= off) v += n;
+  }
+  __syncthreads();  // wsum may still be read by a previous scan
+  if (lane == 31) wsum[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    int w = wsum[lane];
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, w, off);
+      if (lane >= off) w += n;
+    }
+    wsum[lane] = w;
+  }
+  __syncthreads();
+  if (warp > 0) v += wsum[warp - 1];
+  return v;
+}
+
+// Position `v` of the reference's visiting order -> element index, when NT
+// threads each walk elements tid, tid+NT, tid+2NT, ... of n elements.
+__device__ __forceinline__ int strided_order(int v, int n, int NT) {
+  const int q = n / NT, r = n % NT;
+  int tid, i;
+  if (v < r * (q + 1)) {
+    tid = v / (q + 1);
+    i = v % (q + 1);
+  } else {
+    const int vv = v - r * (q + 1);
+    tid = r + vv / q;
+    i = vv % q;
+  }
+  return tid + i * NT;
+}
+
+// The sort primitive.  P provides:
+//   int  slots()                       sub-items per position
+//   int  key(int pos, int j)           bucket of sub-item j of position pos, or -1
+//   void emit(int pos, int j, int out) called once per sub-item with key >= 0
+//   void skip(int pos, int j)          called once per sub-item with key < 0
+// Positions 0..n_pos-1 are already in visiting order.  On return s.base/s.total
+// hold the exclusive bucket offsets and the bucket sizes.
+template <class P>
+__device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  const int chunk = ((n_pos + kPlanThreads - 1) / kPlanThreads) * 32;
+  const int p_begin = min(n_pos, warp * chunk), p_end = min(n_pos, p_begin + chunk);
+  const int J = p.slots();
+  for (int i = threadIdx.x; i < kPlanWarps * B; i += kPlanThreads) s.rows[i] = 0;
+  __syncthreads();
+  int32_t* my_row = s.rows + warp * B;
+  for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+    const int pos = p0 + lane;
+    const bool live = pos < p_end;
+    for (int j = 0; j < J; j++) {
+      const int key = live ? p.key(pos, j) : -1;
+      const unsigned m = __match_any_sync(0xffffffffu, key);
+      if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += kPlanThreads) {
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < kPlanWarps; w++) {
+      const int c = s.rows[w * B + b];
+      s.rows[w * B + b] = run;
+      run += c;
+    }
+    s.total[b] = run;
+  }
+  __syncthreads();
+  {
+    const int v = threadIdx.x < B ? s.total[threadIdx.x] : 0;
+    const int inc = block_inclusive_scan(v, s.wsum);
+    if (threadIdx.x < B) s.base[threadIdx.x] = inc - v;
+  }
+  __syncthreads();
+  for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+    const int pos = p0 + lane;
+    const bool live = pos < p_end;
+    for (int j = 0; j < J; j++) {
+      const int key = live ? p.key(pos, j) : -1;
+      const unsigned m = __match_any_sync(0xffffffffu, key);
+      int mine = 0;
+      if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
+      __syncwarp();
+      if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+      __syncwarp();
+      if (live) {
+        if (key >= 0) p.emit(pos, j, mine);
+        else p.skip(pos, j);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// Inclusive count at the end of every (group, stage) run of buckets.
+__device__ __forceinline__ void write_stage_sums(const SortScratch& s, int groups, int EL, int S, int32_t* out) {
+  const int EPS = EL / S;
+  for (int i = threadIdx.x; i < groups * S; i += kPlanThreads) {
+    const int g = i / S, st = i % S;
+    const int last = g * EL + (st + 1) * EPS - 1;
+    out[i] = s.base[last] + s.total[last];
+  }
+}
+
+// ------------------------------------------------------------------ source side: S1 + S5 + S6
+
+struct CommPlanProblem {
+  const int32_t* idx;
+  int32_t* send_map;
+  int T, k, W, EL, NT;
+  __device__ int slots() const { return W; }
+  __device__ int token(int pos) const { return strided_order(pos, T, NT); }
+  __device__ int key(int pos, int ep) const {
+    const int32_t* row = idx + (size_t)token(pos) * k;
+    int lead = INT32_MAX;
+    for (int j = 0; j < k; j++) {
+      const int e = row[j];
+      if (e >= 0 && e / EL == ep) lead = min(lead, e % EL);
+    }
+    return lead == INT32_MAX ? -1 : ep * EL + lead;
+  }
+  __device__ void emit(int pos, int ep, int out) const { send_map[out] = ep * T + token(pos); }
+  __device__ void skip(int, int) const {}
+};
+
+struct GlobalPlanProblem {
+  const int32_t* idx;
+  const int32_t* send_map;
+  int32_t* glob_map;
+  int T, k, W, EL;
+  __device__ int slots() const { return 1; }
+  __device__ int key(int pos, int) const {
+    const int m = send_map[pos];
+    const int ep = m / T, t = m % T;
+    const int32_t* row = idx + (size_t)t * k;
+    int tail = -1;
+    for (int j = 0; j < k; j++) {
+      const int e = row[j];
+      if (e >= 0 && e / EL == ep) tail = max(tail, e % EL);
+    }
+    return tail < 0 ? -1 : ep * EL + tail;
+  }
+  __device__ void emit(int pos, int, int out) const {
+    const int m = send_map[pos];
+    glob_map[(size_t)(m % T) * W + m / T] = out;
+  }
+  __device__ void skip(int, int) const {}
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weights, int T, int k, int E, int W,
+                    int S, int32_t* send_map, int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl,
+                    float* zero_scale) {
+  extern __shared__ int32_t plan_smem[];
+  const int EL = E / W;
+  SortScratch s = carve(plan_smem, E);
+  if (zero_scale != nullptr && weights != nullptr) {
+    for (int t = threadIdx.x; t < T; t += kPlanThreads) {
+      float z = 0.0f;
+      for (int j = 0; j < k; j++)
+        if (idx[(size_t)t * k + j] < 0) z += weights[(size_t)t * k + j];
+      zero_scale[t] = z;
+    }
+  }
+  int NT = (T + 15) / 16;
+  NT = max(1, min(NT, 128));
+  CommPlanProblem cp{idx, send_map, T, k, W, EL, NT};
+  stable_bucket_sort(cp, T, E, s);
+  write_stage_sums(s, W, EL, S, send_incl);
+  if (glob_map == nullptr) return;
+  const int n_sent = s.base[E - 1] + s.total[E - 1];
+  for (int i = threadIdx.x; i < T * W; i += kPlanThreads) glob_map[i] = T * W;
+  __syncthreads();  // send_map and the glob_map fill are visible to the whole CTA
+  GlobalPlanProblem gp{idx, send_map, glob_map, T, k, W, EL};
+  stable_bucket_sort(gp, n_sent, E, s);
+  write_stage_sums(s, W, EL, S, coll_incl);
+}
+
+// ------------------------------------------------------------------ S2 receive plan
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+recv_plan_kernel(const int32_t* __restrict__ gathered, int my_rank, int W, int S, int32_t* recv_incl,
+                 int32_t* remote_offset, int32_t* total_rows) {
+  __shared__ int32_t wsum[kPlanWarps + 1];
+  const int n = W * S;
+  const int i = threadIdx.x;
+  for (int rank = 0; rank < W; rank++) {
+    int cnt = 0;
+    if (i < n) {
+      const int stage = i % S, dev = i / S;
+      const int begin = (rank == 0 && stage == 0) ? 0 : gathered[(size_t)dev * n + rank * S + stage - 1];
+      cnt = gathered[(size_t)dev * n + rank * S + stage] - begin;
+    }
+    const int inc = block_inclusive_scan(cnt, wsum);
+    if (i < n) {
+      if (rank == my_rank) {
+        recv_incl[i] = inc;
+        if (i == n - 1 && total_rows != nullptr) *total_rows = inc;
+      }
+      if (i / S == my_rank) remote_offset[rank * S + i % S] = inc - cnt;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ expert side: S3 + S4
+
+struct GemmPlanProblem {
+  const int32_t* ridx;
+  int32_t* gemm_map;
+  int32_t* inv_gemm;
+  int R, k, lo, hi, NT;
+  __device__ int slots() const { return k; }
+  __device__ int row(int pos) const { return strided_order(pos, R, NT); }
+  __device__ int key(int pos, int j) const {
+    const int g = ridx[(size_t)row(pos) * k + j];
+    return (lo <= g && g < hi) ? g - lo : -1;
+  }
+  __device__ void emit(int pos, int j, int out) const {
+    const int m = row(pos) * k + j;
+    gemm_map[out] = m;
+    inv_gemm[m] = out;
+  }
+  __device__ void skip(int pos, int j) const { inv_gemm[row(pos) * k + j] = R * k; }
+};
+
+struct LocalReducePlanProblem {
+  const int32_t* ridx;
+  const int32_t* recv_incl;
+  const int32_t* inv_gemm;
+  int32_t* scale_map;
+  int32_t* red_map;
+  int k, lo, hi, W, S, EL;
+  __device__ int slots() const { return 1; }
+  __device__ int key(int r, int) const {
+    int dp = 0;
+    while (dp < W - 1 && r >= recv_incl[dp * S + S - 1]) dp++;
+    int tail = -1;
+    for (int j = 0; j < k; j++) {
+      const int g = ridx[(size_t)r * k + j];
+      if (lo <= g && g < hi) tail = max(tail, g - lo);
+    }
+    return tail < 0 ? -1 : dp * EL + tail;
+  }
+  __device__ void emit(int r, int, int out) const {
+    scale_map[out] = r;
+    for (int j = 0; j < k; j++) red_map[(size_t)out * k + j] = inv_gemm[(size_t)r * k + j];
+  }
+  __device__ void skip(int, int) const {}
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+expert_plans_kernel(const int32_t* __restrict__ ridx, const int32_t* __restrict__ recv_incl, int k, int lo, int hi,
+                    int W, int S, int NT, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm, int32_t* scale_map,
+                    int32_t* red_map, int32_t* ret_incl) {
+  extern __shared__ int32_t plan_smem[];
+  const int EL = hi - lo;
+  const int R = recv_incl[W * S - 1];
+  {
+    SortScratch s = carve(plan_smem, EL);
+    GemmPlanProblem gp{ridx, gemm_map, inv_gemm, R, k, lo, hi, NT};
+    stable_bucket_sort(gp, R, EL, s);
+    for (int e = threadIdx.x; e < EL; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
+    if (threadIdx.x == 0) excl[0] = 0;
+  }
+  if (scale_map == nullptr) return;
+  __syncthreads();  // inv_gemm is complete and visible
+  SortScratch s = carve(plan_smem, W * EL);
+  LocalReducePlanProblem lp{ridx, recv_incl, inv_gemm, scale_map, red_map, k, lo, hi, W, S, EL};
+  stable_bucket_sort(lp, R, W * EL, s);
+  write_stage_sums(s, W, EL, S, ret_incl);
+}
+
+// ------------------------------------------------------------------ fast_ep: F1, F2
+
+struct FastEpExpandProblem {
+  const int32_t* idx;
+  int32_t* mapping;
+  const int32_t* base;   // shared memory: exclusive offset of every expert
+  const int32_t* total;  // shared memory: rows of every expert
+  int k;
+  __device__ int slots() const { return k; }
+  __device__ int key(int t, int j) const {
+    const int e = idx[(size_t)t * k + j];
+    return e >= 0 ? e : -1;
+  }
+  // `out` = base + ascending rank; the reference hands slots out from the end of the expert's range.
+  __device__ void emit(int t, int j, int out) const {
+    const int e = idx[(size_t)t * k + j];
+    mapping[(size_t)t * k + j] = base[e] + total[e] - 1 - (out - base[e]);
+  }
+  __device__ void skip(int t, int j) const { mapping[(size_t)t * k + j] = t + kZcMark; }
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+fastep_expand_plan_kernel(const int32_t* __restrict__ idx, int T, int k, int E, int32_t* excl, int32_t* mapping) {
+  extern __shared__ int32_t plan_smem[];
+  SortScratch s = carve(plan_smem, E);
+  FastEpExpandProblem fp{idx, mapping, s.base, s.total, k};
+  stable_bucket_sort(fp, T, E, s);
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
+  if (threadIdx.x == 0) excl[0] = 0;
+}
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+fastep_plan_kernel(const int32_t* __restrict__ ag, int my_rank, int W, int E, int32_t* remote_recv_plan,
+                   int32_t* local_send_plan, int32_t* gemm_plan, int32_t* arr_src, int32_t* arr_rows,
+                   int32_t* arr_dst) {
+  __shared__ int32_t wsum[kPlanWarps + 1];
+  const int EL = E / W;
+  const int tid = threadIdx.x;
+  const size_t stride = (size_t)E + 1;
+  // rows each source rank sends to each of my local experts: index (i = local expert, j = source rank)
+  // expert-major order p = i*W + j gives arr_dst / gemm_plan; source-major order gives arr_src.
+  {
+    const int i = tid / W, j = tid % W;
+    int rows = 0;
+    if (tid < EL * W) {
+      const size_t pos = stride * j + (size_t)my_rank * EL + i;
+      rows = ag[pos + 1] - ag[pos];
+    }
+    const int inc = block_inclusive_scan(rows, wsum);
+    if (tid < EL * W) {
+      arr_dst[tid] = inc - rows;
+      arr_rows[tid] = rows;
+      if (j == W - 1) gemm_plan[i + 1] = inc;
+    }
+    if (tid == 0) gemm_plan[0] = 0;
+  }
+  {
+    const int j = tid / EL, i = tid % EL;
+    int rows = 0;
+    if (tid < EL * W) {
+      const size_t pos = stride * j + (size_t)my_rank * EL + i;
+      rows = ag[pos + 1] - ag[pos];
+    }
+    const int inc = block_inclusive_scan(rows, wsum);
+    if (tid < EL * W) {
+      arr_src[i * W + j] = inc - rows;
+      if (i == EL - 1) local_send_plan[j + 1] = inc;
+    }
+    if (tid == 0) local_send_plan[0] = 0;
+  }
+  if (tid < W) {
+    int v = 0;
+    for (int j = 0; j < my_rank; j++) v += ag[stride * j + (size_t)(tid + 1) * EL] - ag[stride * j + (size_t)tid * EL];
+    remote_recv_plan[tid] = v;
+  }
+}
+
+int set_smem(const void* fn, size_t bytes) {
+  if (bytes > 227 * 1024) return fail(EPSB_ERR_INVALID, "plan needs %zu bytes of shared memory (> 227 KB)", bytes);
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return fail(EPSB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  return EPSB_OK;
+}
+
+}  // namespace
+
+}  // namespace epsb
+
+using namespace epsb;
+
+extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, int E, int W, int S,
+                                 int32_t* send_map, int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl,
+                                 float* zero_scale, void* stream) {
+  EPSB_REQUIRE(T >= 0 && k > 0 && E > 0 && W > 0 && S > 0, EPSB_ERR_INVALID, "bad sizes T=%d k=%d E=%d W=%d S=%d", T, k,
+               E, W, S);
+  EPSB_REQUIRE(E % W == 0, EPSB_ERR_INVALID, "num_experts %d is not divisible by ep_world_size %d", E, W);
+  EPSB_REQUIRE((E / W) % S == 0, EPSB_ERR_INVALID, "Invalid num_stages: %d for local_num_experts: %d", S, E / W);
+  EPSB_REQUIRE(E <= kMaxBuckets, EPSB_ERR_INVALID, "num_experts %d exceeds %d", E, kMaxBuckets);
+  EPSB_REQUIRE((glob_map == nullptr) == (coll_incl == nullptr), EPSB_ERR_INVALID,
+               "glob_map and coll_incl go together");
+  auto st = static_cast<cudaStream_t>(stream);
+  if (T == 0) {  // reference: comm_expander_ver2.cu:175-178, global_reducer_ver2.cu:207-210
+    cudaMemsetAsync(send_incl, 0, sizeof(int32_t) * W * S, st);
+    if (coll_incl) cudaMemsetAsync(coll_incl, 0, sizeof(int32_t) * W * S, st);
+    return check_launch("source_plans(T=0)");
+  }
+  const size_t smem = sort_smem_bytes(E);
+  int rc = set_smem((const void*)source_plans_kernel, smem);
+  if (rc) return rc;
+  source_plans_kernel<<<1, kPlanThreads, smem, st>>>(idx, weights, T, k, E, W, S, send_map, send_incl, glob_map,
+                                                     coll_incl, zero_scale);
+  return check_launch("source_plans");
+}
+
+extern "C" int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S, int32_t* recv_incl,
+                              int32_t* remote_offset, int32_t* total_rows, void* stream) {
+  EPSB_REQUIRE(W > 0 && S > 0 && my_rank >= 0 && my_rank < W, EPSB_ERR_INVALID, "bad rank/world %d/%d", my_rank, W);
+  EPSB_REQUIRE(W * S <= kPlanThreads, EPSB_ERR_INVALID, "ep_world_size * num_stages is too big.");
+  recv_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(gathered, my_rank, W, S, recv_incl,
+                                                                              remote_offset, total_rows);
+  return check_launch("recv_plan");
+}
+
+extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
+                                 int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map,
+                                 int32_t* inv_gemm, int32_t* scale_map, int32_t* red_map, int32_t* ret_incl,
+                                 void* stream) {
+  const int EL = hi - lo;
+  EPSB_REQUIRE(EL > 0 && k > 0 && W > 0 && S > 0, EPSB_ERR_INVALID, "bad sizes EL=%d k=%d W=%d S=%d", EL, k, W, S);
+  EPSB_REQUIRE(EL % S == 0, EPSB_ERR_INVALID, "Invalid num_stages: %d for local_num_experts: %d", S, EL);
+  EPSB_REQUIRE((int64_t)W * EL <= kMaxBuckets, EPSB_ERR_INVALID, "W*EL = %lld exceeds %d", (long long)W * EL,
+               kMaxBuckets);
+  EPSB_REQUIRE(max_rows * k < (1ll << 31), EPSB_ERR_INVALID, "max_rows*k overflows int32");
+  EPSB_REQUIRE((scale_map == nullptr) == (red_map == nullptr) && (scale_map == nullptr) == (ret_incl == nullptr),
+               EPSB_ERR_INVALID, "scale_map, red_map and ret_incl go together");
+  int64_t tot = (int64_t)max_tok_per_gpu * W;
+  int NT = (int)((tot + 15) / 16);
+  if (NT > 128) NT = 128;
+  if (NT < 1) NT = 1;
+  const size_t smem = sort_smem_bytes(scale_map ? W * EL : EL);
+  int rc = set_smem((const void*)expert_plans_kernel, smem);
+  if (rc) return rc;
+  expert_plans_kernel<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      ridx, recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl);
+  return check_launch("expert_plans");
+}
+
+extern "C" int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, int32_t* excl, int32_t* mapping,
+                                       void* stream) {
+  EPSB_REQUIRE(T >= 0 && k > 0 && E > 0 && E <= kMaxBuckets, EPSB_ERR_INVALID, "bad sizes T=%d k=%d E=%d", T, k, E);
+  const size_t smem = sort_smem_bytes(E);
+  int rc = set_smem((const void*)fastep_expand_plan_kernel, smem);
+  if (rc) return rc;
+  fastep_expand_plan_kernel<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(idx, T, k, E, excl, mapping);
+  return check_launch("fastep_expand_plan");
+}
+
+extern "C" int epsb_fastep_plan(const int32_t* all_gathered, int my_rank, int W, int E, int32_t* remote_recv_plan,
+                                int32_t* local_send_plan, int32_t* gemm_plan, int32_t* arr_src, int32_t* arr_rows,
+                                int32_t* arr_dst, void* stream) {
+  EPSB_REQUIRE(W > 0 && E > 0 && E % W == 0 && my_rank >= 0 && my_rank < W, EPSB_ERR_INVALID,
+               "bad sizes W=%d E=%d rank=%d", W, E, my_rank);
+  EPSB_REQUIRE(E <= kPlanThreads, EPSB_ERR_INVALID, "num_experts %d exceeds %d", E, kPlanThreads);
+  fastep_plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      all_gathered, my_rank, W, E, remote_recv_plan, local_send_plan, gemm_plan, arr_src, arr_rows, arr_dst);
+  return check_launch("fastep_plan");
+}

@@ -1,0 +1,231 @@
+// Per-token 1x128 and per-block 128x128 FP8 (e4m3) quantisation for sm_100a.
+//
+// Replaces per_token_group_quant_fp8 (reference src/quant/fp8.cu:247-382).  The
+// reference gives one 16-lane tile a group and one CTA a row; here the
+// (row, group) pairs are flattened over a grid sized to the SM count, each
+// half-warp owns a group (16 B per lane in, 8 B per lane out), and every lane
+// keeps several groups in flight so that the kernel is bound by HBM, not by
+// load latency.
+#include "common.cuh"
+
+namespace epsb {
+
+namespace {
+
+constexpr int kQuantThreads = 256;
+constexpr int kUnroll = 4;  // groups in flight per half-warp
+
+template <bool kDivFull>
+__device__ __forceinline__ void quant_group_store(uint4 v, int sub, bool live, uint8_t* qdst, float* sdst) {
+  float f[8];
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+  f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+  f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(f[i]));
+  // 16-lane butterfly; xor offsets < 16 never cross the half-warp.
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float scale = scale_of_amax<kDivFull>(amax);
+  const float inv = __frcp_rn(scale);
+  uint2 out;
+  out.x = (uint32_t)cvt_e4m3x2(quant_clamp(f[0], inv), quant_clamp(f[1], inv)) |
+          ((uint32_t)cvt_e4m3x2(quant_clamp(f[2], inv), quant_clamp(f[3], inv)) << 16);
+  out.y = (uint32_t)cvt_e4m3x2(quant_clamp(f[4], inv), quant_clamp(f[5], inv)) |
+          ((uint32_t)cvt_e4m3x2(quant_clamp(f[6], inv), quant_clamp(f[7], inv)) << 16);
+  if (live) {
+    *reinterpret_cast<uint2*>(qdst + sub * 8) = out;
+    if (sub == 0) *sdst = scale;
+  }
+}
+
+// One "task" = one 128-column group of one row; a warp takes two adjacent tasks
+// (512 contiguous bytes of a row), one per half-warp.
+template <bool kDivFull>
+__global__ void __launch_bounds__(kQuantThreads)
+quant_1x128_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales,
+                   const int32_t* __restrict__ bounds, int num_experts, int64_t rows, int64_t groups_per_row) {
+  int64_t row0 = 0;
+  if (bounds != nullptr) {
+    row0 = bounds[0];
+    rows = (int64_t)bounds[num_experts] - row0;
+  }
+  const int64_t n_tasks = rows * groups_per_row;
+  const int64_t n_pairs = (n_tasks + 1) >> 1;
+  const int lane = threadIdx.x & 31;
+  const int half = lane >> 4, sub = lane & 15;
+  const int64_t wid = ((int64_t)blockIdx.x * kQuantThreads + threadIdx.x) >> 5;
+  const int64_t n_w = ((int64_t)gridDim.x * kQuantThreads) >> 5;
+  const int64_t base = row0 * groups_per_row;
+  for (int64_t p0 = wid; p0 < n_pairs; p0 += n_w * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const int64_t t = 2 * (p0 + (int64_t)u * n_w) + half;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (t < n_tasks) v[u] = ld_nc_16(x + (base + t) * 128 + sub * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const int64_t p = p0 + (int64_t)u * n_w;
+      if (p < n_pairs) {  // warp-uniform: the shuffles inside need all 32 lanes
+        const int64_t t = 2 * p + half;
+        quant_group_store<kDivFull>(v[u], sub, t < n_tasks, q + (base + t) * 128, scales + base + t);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kQuantThreads)
+dequant_1x128_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales, uint16_t* __restrict__ x,
+                     int64_t n_tasks) {
+  const int sub = threadIdx.x & 15;
+  const int64_t hw = ((int64_t)blockIdx.x * kQuantThreads + threadIdx.x) >> 4;
+  const int64_t n_hw = ((int64_t)gridDim.x * kQuantThreads) >> 4;
+  for (int64_t t = hw; t < n_tasks; t += n_hw) {
+    const uint2 c = *reinterpret_cast<const uint2*>(q + t * 128 + sub * 8);
+    const float s = scales[t];
+    const uint8_t* cb = reinterpret_cast<const uint8_t*>(&c);
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      __nv_fp8_e4m3 e;
+      e.__x = cb[i];
+      f[i] = static_cast<float>(e) * s;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(f[0], f[1]);
+    o.y = pack_bf16x2(f[2], f[3]);
+    o.z = pack_bf16x2(f[4], f[5]);
+    o.w = pack_bf16x2(f[6], f[7]);
+    st_16(x + t * 128 + sub * 8, o);
+  }
+}
+
+// One CTA per 128x128 block of one matrix: 256 threads, thread (r16, c) = 16 rows x
+// 16-byte column pieces.  Two passes over a 32 KB block that stays in L1/L2.
+__global__ void __launch_bounds__(256)
+quant_block128_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ q, float* __restrict__ scales,
+                      int64_t n, int64_t k, int64_t nb, int64_t kb) {
+  const int64_t blk = blockIdx.x;
+  const int64_t mat = blk / (nb * kb);
+  const int64_t bi = (blk / kb) % nb;
+  const int64_t bj = blk % kb;
+  const uint16_t* wm = w + mat * n * k;
+  uint8_t* qm = q + mat * n * k;
+  const int c8 = (threadIdx.x & 15) * 8;  // column offset inside the block
+  const int r0 = threadIdx.x >> 4;        // 0..15
+  const int64_t col = bj * 128 + c8;
+  const bool col_ok = col < k;            // k % 8 == 0, so a live piece is fully inside
+  float amax = 0.0f;
+  uint4 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int64_t row = bi * 128 + r0 + i * 16;
+    v[i] = make_uint4(0, 0, 0, 0);
+    if (col_ok && row < n) v[i] = ld_nc_16(wm + row * k + col);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf16_lo(v[i].x)), fabsf(bf16_hi(v[i].x))),
+                             fmaxf(fabsf(bf16_lo(v[i].y)), fabsf(bf16_hi(v[i].y)))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf16_lo(v[i].z)), fabsf(bf16_hi(v[i].z))),
+                             fmaxf(fabsf(bf16_lo(v[i].w)), fabsf(bf16_hi(v[i].w)))));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  __shared__ float warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int i = 1; i < 8; i++) amax = fmaxf(amax, warp_max[i]);
+  const float scale = __fdiv_rn(amax, kFp8Max);
+  const float inv = __frcp_rn(scale);
+  if (threadIdx.x == 0) scales[blk] = scale;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int64_t row = bi * 128 + r0 + i * 16;
+    if (col_ok && row < n) {
+      uint2 o;
+      o.x = (uint32_t)cvt_e4m3x2(quant_clamp(bf16_lo(v[i].x), inv), quant_clamp(bf16_hi(v[i].x), inv)) |
+            ((uint32_t)cvt_e4m3x2(quant_clamp(bf16_lo(v[i].y), inv), quant_clamp(bf16_hi(v[i].y), inv)) << 16);
+      o.y = (uint32_t)cvt_e4m3x2(quant_clamp(bf16_lo(v[i].z), inv), quant_clamp(bf16_hi(v[i].z), inv)) |
+            ((uint32_t)cvt_e4m3x2(quant_clamp(bf16_lo(v[i].w), inv), quant_clamp(bf16_hi(v[i].w), inv)) << 16);
+      *reinterpret_cast<uint2*>(qm + row * k + col) = o;
+    }
+  }
+}
+
+int quant_grid(int64_t n_tasks) {
+  const int64_t per_block = kQuantThreads / 16;  // tasks per CTA per unrolled step
+  int64_t want = (n_tasks + per_block * kUnroll - 1) / (per_block * kUnroll);
+  const int64_t cap = (int64_t)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+}  // namespace
+
+}  // namespace epsb
+
+using namespace epsb;
+
+extern "C" int epsb_quant_1x128(const void* x, int64_t rows, int64_t cols, void* q, float* scales, int div_mode,
+                                void* stream) {
+  EPSB_REQUIRE(cols > 0 && cols % 128 == 0, EPSB_ERR_INVALID, "cols: %lld is not divisible by group_size: 128",
+               (long long)cols);
+  EPSB_REQUIRE(rows >= 0, EPSB_ERR_INVALID, "rows: %lld is negative", (long long)rows);
+  EPSB_REQUIRE(div_mode == 0 || div_mode == 1, EPSB_ERR_INVALID, "div_mode: %d is not 0 or 1", div_mode);
+  if (rows == 0) return EPSB_OK;
+  const int64_t gpr = cols / 128;
+  const int grid = quant_grid(rows * gpr);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (div_mode == 0)
+    quant_1x128_kernel<false><<<grid, kQuantThreads, 0, s>>>((const uint16_t*)x, (uint8_t*)q, scales, nullptr, 0, rows, gpr);
+  else
+    quant_1x128_kernel<true><<<grid, kQuantThreads, 0, s>>>((const uint16_t*)x, (uint8_t*)q, scales, nullptr, 0, rows, gpr);
+  return check_launch("quant_1x128");
+}
+
+extern "C" int epsb_quant_1x128_ragged(const void* x, const int32_t* exclusive_sum, int num_experts, int64_t cols,
+                                       void* q, float* scales, int64_t max_rows, int div_mode, void* stream) {
+  EPSB_REQUIRE(cols > 0 && cols % 128 == 0, EPSB_ERR_INVALID, "cols: %lld is not divisible by group_size: 128",
+               (long long)cols);
+  EPSB_REQUIRE(exclusive_sum != nullptr && num_experts >= 0, EPSB_ERR_INVALID, "exclusive_sum is required");
+  EPSB_REQUIRE(div_mode == 0 || div_mode == 1, EPSB_ERR_INVALID, "div_mode: %d is not 0 or 1", div_mode);
+  if (max_rows <= 0) return EPSB_OK;
+  const int64_t gpr = cols / 128;
+  const int grid = quant_grid(max_rows * gpr);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (div_mode == 0)
+    quant_1x128_kernel<false><<<grid, kQuantThreads, 0, s>>>((const uint16_t*)x, (uint8_t*)q, scales, exclusive_sum, num_experts, 0, gpr);
+  else
+    quant_1x128_kernel<true><<<grid, kQuantThreads, 0, s>>>((const uint16_t*)x, (uint8_t*)q, scales, exclusive_sum, num_experts, 0, gpr);
+  return check_launch("quant_1x128_ragged");
+}
+
+extern "C" int epsb_dequant_1x128(const void* q, const float* scales, int64_t rows, int64_t cols, void* x,
+                                  void* stream) {
+  EPSB_REQUIRE(cols > 0 && cols % 128 == 0, EPSB_ERR_INVALID, "cols: %lld is not divisible by group_size: 128",
+               (long long)cols);
+  if (rows <= 0) return EPSB_OK;
+  const int64_t n_tasks = rows * (cols / 128);
+  const int grid = quant_grid(n_tasks);
+  dequant_1x128_kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>((const uint8_t*)q, scales,
+                                                                                      (uint16_t*)x, n_tasks);
+  return check_launch("dequant_1x128");
+}
+
+extern "C" int epsb_quant_block128(const void* w, int64_t n_mats, int64_t n, int64_t k, void* q, float* scales,
+                                   void* stream) {
+  EPSB_REQUIRE(n > 0 && k > 0 && k % 16 == 0, EPSB_ERR_INVALID, "weight shape [%lld,%lld] needs k %% 16 == 0",
+               (long long)n, (long long)k);
+  if (n_mats <= 0) return EPSB_OK;
+  const int64_t nb = (n + 127) / 128, kb = (k + 127) / 128;
+  const int64_t blocks = n_mats * nb * kb;
+  EPSB_REQUIRE(blocks < (1ll << 31), EPSB_ERR_INVALID, "too many weight blocks: %lld", (long long)blocks);
+  quant_block128_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint16_t*)w, (uint8_t*)q, scales, n, k, nb, kb);
+  return check_launch("quant_block128");
+}

@@ -1,0 +1,263 @@
+"""Tensor-level operators over the C ABI (include/eps_b200.h).
+
+Each function checks its tensors the way the reference's bindings do
+(device / contiguity / dtype, reference src/common/torch_utils.h:39-44), passes
+raw pointers to libeps_b200.so and launches on the current CUDA stream
+(reference bindings use at::cuda::getCurrentCUDAStream()).  torch is used for
+device memory and streams only.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import EpsError, call, ptr, stream_ptr
+
+GEMM_PLAIN, GEMM_GATEUP, GEMM_DOWN = 0, 1, 2
+ZC_MARK = 1000000
+INT32_MAX = 2**31 - 1
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dim=None):
+    if not t.is_cuda:
+        raise EpsError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise EpsError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise EpsError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise EpsError(f"{name} must have {dim} dimensions, got {t.dim()}")
+
+
+_FP8 = (torch.uint8, torch.float8_e4m3fn)
+
+# ------------------------------------------------------------------ quantisation
+
+
+def per_token_group_quant_fp8(x, exclusive_sum=None, num_experts=0, div_mode=0, out=None, out_scales=None):
+    """x [rows, cols] bf16 -> (codes uint8 [rows, cols], scales fp32 [rows, cols/128]).
+
+    With `exclusive_sum` only rows [exclusive_sum[0], exclusive_sum[num_experts]) are written
+    (reference PerTokenGroupQuantFP8Params, src/quant/fp8.cuh:43-57)."""
+    _check(x, "x", torch.bfloat16, 2)
+    rows, cols = x.shape
+    q = out if out is not None else torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    s = out_scales if out_scales is not None else torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
+    if exclusive_sum is None:
+        call("epsb_quant_1x128", ptr(x), rows, cols, ptr(q), ptr(s), div_mode, stream_ptr())
+    else:
+        _check(exclusive_sum, "exclusive_sum", torch.int32, 1)
+        call("epsb_quant_1x128_ragged", ptr(x), ptr(exclusive_sum), num_experts, cols, ptr(q), ptr(s), rows,
+             div_mode, stream_ptr())
+    return q, s
+
+
+def per_token_group_dequant_fp8(q, scales):
+    _check(q, "q", _FP8, 2)
+    _check(scales, "scales", torch.float32, 2)
+    rows, cols = q.shape
+    x = torch.empty((rows, cols), dtype=torch.bfloat16, device=q.device)
+    call("epsb_dequant_1x128", ptr(q), ptr(scales), rows, cols, ptr(x), stream_ptr())
+    return x
+
+
+def quant_block128(w):
+    """w [n_mats, n, k] (or [n, k]) bf16 -> (codes uint8, scales fp32 [n_mats, ceil(n/128), ceil(k/128)])."""
+    _check(w, "w", torch.bfloat16)
+    squeeze = w.dim() == 2
+    w3 = w.unsqueeze(0) if squeeze else w
+    m, n, k = w3.shape
+    q = torch.empty((m, n, k), dtype=torch.uint8, device=w.device)
+    s = torch.empty((m, (n + 127) // 128, (k + 127) // 128), dtype=torch.float32, device=w.device)
+    call("epsb_quant_block128", ptr(w3), m, n, k, ptr(q), ptr(s), stream_ptr())
+    return (q[0], s[0]) if squeeze else (q, s)
+
+
+# ------------------------------------------------------------------ plans
+
+
+def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True):
+    _check(idx, "expert_indices", torch.int32, 2)
+    T, k = idx.shape
+    dev = idx.device
+    send_map = torch.empty((max(T * W, 1),), dtype=torch.int32, device=dev)
+    send_incl = torch.empty((W * S,), dtype=torch.int32, device=dev)
+    glob_map = torch.empty((max(T * W, 1),), dtype=torch.int32, device=dev) if want_global else None
+    coll_incl = torch.empty((W * S,), dtype=torch.int32, device=dev) if want_global else None
+    zero_scale = None
+    if want_zero and weights is not None:
+        _check(weights, "expert_scales", torch.float32, 2)
+        zero_scale = torch.empty((max(T, 1),), dtype=torch.float32, device=dev)
+    call("epsb_source_plans", ptr(idx), ptr(weights), T, k, E, W, S, ptr(send_map), ptr(send_incl), ptr(glob_map),
+         ptr(coll_incl), ptr(zero_scale), stream_ptr())
+    return send_map, send_incl, glob_map, coll_incl, zero_scale
+
+
+def recv_plan(gathered, my_rank, W, S, total_rows=None):
+    _check(gathered, "gathered_send_plan", torch.int32)
+    dev = gathered.device
+    recv_incl = torch.empty((W * S,), dtype=torch.int32, device=dev)
+    remote_offset = torch.empty((W * S,), dtype=torch.int32, device=dev)
+    call("epsb_recv_plan", ptr(gathered), my_rank, W, S, ptr(recv_incl), ptr(remote_offset), ptr(total_rows),
+         stream_ptr())
+    return recv_incl, remote_offset
+
+
+def expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, want_reduce=True):
+    _check(ridx, "recv_expert_indices", torch.int32)
+    _check(recv_incl, "recv_plan", torch.int32, 1)
+    dev = ridx.device
+    EL = hi - lo
+    n = max(max_rows * k, 1)
+    excl = torch.empty((EL + 1,), dtype=torch.int32, device=dev)
+    gemm_map = torch.empty((n,), dtype=torch.int32, device=dev)
+    inv_gemm = torch.empty((n,), dtype=torch.int32, device=dev)
+    scale_map = red_map = ret_incl = None
+    if want_reduce:
+        scale_map = torch.empty((max(max_rows, 1),), dtype=torch.int32, device=dev)
+        red_map = torch.empty((n,), dtype=torch.int32, device=dev)
+        ret_incl = torch.empty((W * S,), dtype=torch.int32, device=dev)
+    call("epsb_expert_plans", ptr(ridx), ptr(recv_incl), k, lo, hi, W, S, max_tok_per_gpu, max_rows, ptr(excl),
+         ptr(gemm_map), ptr(inv_gemm), ptr(scale_map), ptr(red_map), ptr(ret_incl), stream_ptr())
+    return excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl
+
+
+def fastep_expand_plan(idx, E, excl=None):
+    _check(idx, "expert_indices", torch.int32, 2)
+    T, k = idx.shape
+    if excl is None:
+        excl = torch.empty((E + 1,), dtype=torch.int32, device=idx.device)
+    mapping = torch.empty((max(T * k, 1),), dtype=torch.int32, device=idx.device)
+    call("epsb_fastep_expand_plan", ptr(idx), T, k, E, ptr(excl), ptr(mapping), stream_ptr())
+    return excl, mapping
+
+
+def fastep_plan(all_gathered, my_rank, W, E, gemm_plan=None):
+    _check(all_gathered, "all_gathered", torch.int32)
+    dev = all_gathered.device
+    EL = E // W
+    remote_recv = torch.empty((W,), dtype=torch.int32, device=dev)
+    local_send = torch.empty((W + 1,), dtype=torch.int32, device=dev)
+    if gemm_plan is None:
+        gemm_plan = torch.empty((EL + 1,), dtype=torch.int32, device=dev)
+    arr = torch.empty((3, EL * W), dtype=torch.int32, device=dev)
+    call("epsb_fastep_plan", ptr(all_gathered), my_rank, W, E, ptr(remote_recv), ptr(local_send), ptr(gemm_plan),
+         ptr(arr[0]), ptr(arr[1]), ptr(arr[2]), stream_ptr())
+    return remote_recv, local_send, gemm_plan, arr[0], arr[1], arr[2]
+
+
+# ------------------------------------------------------------------ row movement
+
+
+def _row_bytes(t):
+    return t.shape[-1] * t.element_size()
+
+
+def gather_rows(src, dst, mapping, map_div=1, map_mod=INT32_MAX, bounds=None, b0=0, b1=0, n_rows=None):
+    """dst[i] = src[(mapping[i] // map_div) % map_mod]; rows [bounds[b0], bounds[b1]) or [0, n_rows)."""
+    _check(src, "src")
+    _check(dst, "dst")
+    if _row_bytes(src) != _row_bytes(dst):
+        raise EpsError("src and dst rows differ in size")
+    max_rows = dst.shape[0]
+    n = max_rows if n_rows is None else n_rows
+    call("epsb_gather_rows", ptr(src), ptr(dst), ptr(mapping), map_div, map_mod, ptr(bounds), b0, b1, n, max_rows,
+         _row_bytes(src), stream_ptr())
+    return dst
+
+
+def scatter_rows(src, dst, mapping, div, n):
+    _check(src, "src")
+    _check(dst, "dst")
+    call("epsb_scatter_rows", ptr(src), ptr(dst), ptr(mapping), div, n, _row_bytes(src), stream_ptr())
+    return dst
+
+
+def arrange_rows(src, dst, src_off, rows, dst_off, n_seg, max_rows):
+    _check(src, "src")
+    _check(dst, "dst")
+    call("epsb_arrange_rows", ptr(src), ptr(dst), ptr(src_off), ptr(rows), ptr(dst_off), n_seg, max_rows,
+         _row_bytes(src), stream_ptr())
+    return dst
+
+
+def gather_row_weights(w_recv, gemm_map, excl, num_experts, max_rows):
+    row_w = torch.empty((max(max_rows, 1),), dtype=torch.float32, device=w_recv.device)
+    call("epsb_gather_row_weights", ptr(w_recv), ptr(gemm_map), ptr(excl), num_experts, max_rows, ptr(row_w),
+         stream_ptr())
+    return row_w
+
+
+# ------------------------------------------------------------------ reductions
+
+
+def local_reduce_ref(y, w_recv, scale_map, red_map, ret_incl, k, W, S, stage, send, max_rows=None):
+    _check(y, "gemm_output", torch.bfloat16, 2)
+    _check(send, "send_buf", torch.bfloat16, 2)
+    H = y.shape[1]
+    call("epsb_local_reduce_ref", ptr(y), ptr(w_recv), ptr(scale_map), ptr(red_map), ptr(ret_incl), k, W, S, stage,
+         send.shape[0] if max_rows is None else max_rows, H, ptr(send), stream_ptr())
+    return send
+
+
+def local_reduce(y, red_map, ret_incl, k, W, S, stage, send, max_rows=None):
+    _check(y, "gemm_output", torch.bfloat16, 2)
+    _check(send, "send_buf", torch.bfloat16, 2)
+    H = y.shape[1]
+    call("epsb_local_reduce", ptr(y), ptr(red_map), ptr(ret_incl), k, W, S, stage,
+         send.shape[0] if max_rows is None else max_rows, H, ptr(send), stream_ptr())
+    return send
+
+
+def global_reduce(recv, glob_map, out, W, shared=None, x=None, zero_scale=None, ref_arith=False):
+    _check(out, "output", torch.bfloat16, 2)
+    T, H = out.shape
+    name = "epsb_global_reduce_ref" if ref_arith else "epsb_global_reduce"
+    call(name, ptr(recv), ptr(glob_map), ptr(shared), ptr(x), ptr(zero_scale), T, W, H, ptr(out), stream_ptr())
+    return out
+
+
+def fastep_reduce(rows, raw, w, mapping, out, shared=None):
+    _check(out, "out_tokens", torch.bfloat16, 2)
+    _check(w, "weights", torch.float32, 2)
+    T, H = out.shape
+    k = w.shape[1]
+    call("epsb_fastep_reduce", ptr(rows), ptr(raw), ptr(shared), ptr(w), ptr(mapping), T, k, H, ptr(out),
+         stream_ptr())
+    return out
+
+
+def silu_run(gate_up, result, exclusive_sum=None, num_experts=0):
+    _check(gate_up, "gate_up", torch.bfloat16, 2)
+    _check(result, "result", torch.bfloat16, 2)
+    rows, two_i = gate_up.shape
+    call("epsb_silu_run", ptr(gate_up), ptr(result), ptr(exclusive_sum), num_experts, rows, two_i // 2, stream_ptr())
+    return result
+
+
+# ------------------------------------------------------------------ grouped GEMM
+
+
+def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None):
+    """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes."""
+    _check(A, "A", _FP8, 2)
+    _check(a_s, "A_scale", torch.float32, 2)
+    _check(B, "B", _FP8, 3)
+    _check(b_s, "B_scale", torch.float32, 3)
+    _check(excl, "exclusive_sum", torch.int32, 1)
+    max_rows, K = A.shape
+    E, N, K2 = B.shape
+    if K2 != K:
+        raise EpsError(f"A has K={K} but B has K={K2}")
+    if excl.numel() != E + 1:
+        raise EpsError(f"exclusive_sum must have {E + 1} entries")
+    dev = A.device
+    if mode == GEMM_GATEUP:
+        I = N // 2
+        C = out if out is not None else torch.empty((max_rows, I), dtype=torch.uint8, device=dev)
+        c_s = out_scales if out_scales is not None else torch.empty((max_rows, I // 128), dtype=torch.float32, device=dev)
+    else:
+        C = out if out is not None else torch.empty((max_rows, N), dtype=torch.bfloat16, device=dev)
+        c_s = None
+    call("epsb_grouped_gemm_fp8", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K, ptr(C),
+         ptr(c_s), ptr(row_w), ptr(status), stream_ptr())
+    return (C, c_s) if mode == GEMM_GATEUP else C

@@ -1,0 +1,231 @@
+/*
+ * eps_b200 — C ABI of the B200 (sm_100a) FP8 MoE expert-layer kernels.
+ *
+ * This is the boundary a binding of the reference (meituan-longcat/eps) would
+ * call instead of its own CUDA: plain pointers and sizes, no torch types.
+ * Every pointer is a DEVICE pointer unless its comment says "host".  `stream`
+ * is a cudaStream_t passed as void*.  Every function returns EPSB_OK (0) or an
+ * EPSB_ERR_* code; epsb_last_error() then returns a message for the calling
+ * thread.  Launches are asynchronous on `stream`; nothing here synchronises
+ * unless stated.  No function allocates device memory unless stated.
+ *
+ * Citations "ref: path:line" are paths inside the reference repository and
+ * name the interface each entry point replaces.
+ *
+ * Index conventions (identical to the reference): T local tokens, k = top-k,
+ * E routed FFN experts, W expert-parallel world size, EL = E/W local experts,
+ * S stages (S divides EL), R rows received by a rank, D expanded GEMM rows.
+ * A negative expert id is a zero-computation (identity) expert.
+ */
+#ifndef EPS_B200_H_
+#define EPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EPSB_OK 0
+#define EPSB_ERR_INVALID 1  /* bad argument / unsupported shape (reference: std::runtime_error) */
+#define EPSB_ERR_CUDA 2     /* a CUDA runtime/driver call failed */
+#define EPSB_ERR_TIMEOUT 3  /* a bounded device-side wait gave up (see epsb_gemm_status) */
+#define EPSB_ERR_WORKSPACE 4 /* workspace too small */
+
+const char* epsb_last_error(void);
+int epsb_version(void);
+
+/* ----------------------------------------------------------------------------
+ * Quantisation.  ref: src/quant/fp8.cuh:43-72, src/quant/fp8.cu:247-382
+ * (per_token_group_quant_fp8<T,Params>, group_size 128).
+ *
+ * x: [rows, cols] bf16 row-major, cols % 128 == 0.
+ * q: [rows, cols] e4m3 codes.  scales: [rows, cols/128] fp32 row-major.
+ * div_mode 0: scale = amax/448 with IEEE division (the layer contract).
+ * div_mode 1: scale = div.full.f32(amax, 448), the instruction the reference
+ *             kernel uses (fp8.cu:272-275), for bit-parity with that kernel.
+ * -------------------------------------------------------------------------- */
+int epsb_quant_1x128(const void* x, int64_t rows, int64_t cols, void* q, float* scales, int div_mode, void* stream);
+
+/* Ragged form (PerTokenGroupQuantFP8Params, fp8.cuh:43-57): only rows
+ * [exclusive_sum[0], exclusive_sum[num_experts]) are processed; the bounds are
+ * read on the device.  max_rows bounds the grid (reference: num_tokens_hint). */
+int epsb_quant_1x128_ragged(const void* x, const int32_t* exclusive_sum, int num_experts, int64_t cols, void* q,
+                            float* scales, int64_t max_rows, int div_mode, void* stream);
+
+/* Inverse (ref: fp8.cu:299-330): x = bf16(float(code) * scale). */
+int epsb_dequant_1x128(const void* q, const float* scales, int64_t rows, int64_t cols, void* x, void* stream);
+
+/* Weight quantisation: w [n_mats, n, k] bf16 -> codes [n_mats, n, k] and one
+ * fp32 scale per 128x128 block, scales [n_mats, ceil(n/128), ceil(k/128)],
+ * scale = amax/448 (IEEE).  The reference ships no block-scaled weight
+ * quantiser; the slot it fills is GemmInterface::RunParams::weight_scales
+ * (ref: src/scheduler/gemm_executor_interface.cuh:7-10).  k % 16 == 0. */
+int epsb_quant_block128(const void* w, int64_t n_mats, int64_t n, int64_t k, void* q, float* scales, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * EPS scheduler plans.  All emit index layouts bit-identical to the reference.
+ * -------------------------------------------------------------------------- */
+
+/* Source-side plans, one launch.
+ * ref: CommExpander::plan -> getExpandForCommPlanKernel_ver2
+ *      (src/scheduler/comm_expander.cuh:63-85, comm_expander_ver2.cu:30-183);
+ *      GlobalReducer::plan -> getGlobalReducePlanKernel_ver2
+ *      (src/scheduler/global_reducer.cuh:72-100, global_reducer_ver2.cu:31-215);
+ *      ZeroReducer::plan -> zeroReducePlanKernel (src/scheduler/zero_reducer.cu:11-32).
+ * in : idx [T,k] int32, weights [T,k] fp32 (may be NULL -> zero_scale untouched)
+ * out: send_map [T*W] (first send_incl[W*S-1] entries valid) = ep*T + src
+ *      send_incl [W*S] inclusive row counts by (dest rank, stage of leading expert)
+ *      glob_map [T*W]: [t*W+ep] -> row of the returned buffer, or T*W
+ *      coll_incl [W*S] inclusive counts by (dest rank, stage of tailing expert)
+ *      zero_scale [T] = sum of weights of the token's zero-computation slots
+ * Any of glob_map/coll_incl (together) or zero_scale may be NULL to skip. */
+int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, int E, int W, int S, int32_t* send_map,
+                      int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl, float* zero_scale, void* stream);
+
+/* Receive plan from the all-gathered send plans.
+ * ref: AlltoallRunner::plan -> getRecvPlan<512>
+ *      (src/communication/alltoall_runner.cuh:79-103, alltoall_runner.cu:60-101).
+ * gathered [W][W*S]: row d = rank d's inclusive plan.  recv_incl [W*S],
+ * remote_offset [W*S] (where my stage block lands at each peer).
+ * total_rows: optional pointer (device or host-mapped) that receives R. */
+int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S, int32_t* recv_incl, int32_t* remote_offset,
+                   int32_t* total_rows, void* stream);
+
+/* Expert-side plans, one launch.
+ * ref: GemmExpander::plan -> getExpandForGemmPlanKernel_ver2
+ *      (src/scheduler/gemm_expander.cuh:72-103, gemm_expander_ver2.cu:31-186);
+ *      LocalReducer::plan -> getLocalReducePlanKernel_ver2{,_decode}
+ *      (src/scheduler/local_reducer.cuh:78-114, local_reducer_ver2.cu:25-484).
+ * in : ridx [R,k] expert ids of received rows; recv_incl [W*S] (R is read from
+ *      recv_incl[W*S-1] on the device); local experts [lo,hi); max_rows bounds R.
+ * out: excl [EL+1]; gemm_map [max_rows*k] (first excl[EL] valid) = row*k+slot
+ *      inv_gemm [max_rows*k]: [row*k+slot] -> GEMM row or R*k (scratch the
+ *      caller provides; also useful to callers that fuse the gather)
+ *      scale_map [max_rows], red_map [max_rows*k] (sentinel R*k), ret_incl [W*S]
+ * scale_map/red_map/ret_incl may be NULL together to compute only the GEMM plan. */
+int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
+                      int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm,
+                      int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * fast_ep plans.  ref: src/fast_ep/all_to_all/fast_ep_kernels.cu:40-176
+ * (expandPlan) and :352-610 (allGatherPlan + planKernel).
+ * -------------------------------------------------------------------------- */
+int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, int32_t* excl, int32_t* mapping, void* stream);
+int epsb_fastep_plan(const int32_t* all_gathered, int my_rank, int W, int E, int32_t* remote_recv_plan,
+                     int32_t* local_send_plan, int32_t* gemm_plan, int32_t* arr_src, int32_t* arr_rows,
+                     int32_t* arr_dst, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * Row movement.  row_bytes % 16 == 0, all row bases 16-byte aligned.
+ * -------------------------------------------------------------------------- */
+
+/* dst[i,:] = src[(map[i] / map_div) % map_mod, :] for i in [begin, end) where
+ * begin = bounds ? bounds[b0] : 0 and end = bounds ? bounds[b1] : n_rows
+ * (bounds read on the device; max_rows bounds the grid).
+ * ref: expandForComm (src/scheduler/comm_expander.cu:118-215; map_div 1,
+ *      map_mod T) and expandForGemm (src/scheduler/gemm_expander.cu:81-163;
+ *      map_div k, map_mod INT32_MAX, bounds = exclusive_sum). */
+int epsb_gather_rows(const void* src, void* dst, const int32_t* map, int32_t map_div, int32_t map_mod,
+                     const int32_t* bounds, int b0, int b1, int64_t n_rows, int64_t max_rows, int64_t row_bytes,
+                     void* stream);
+
+/* dst[map[i], :] = src[i / div, :] for i < n, skipping map[i] >= 1000000.
+ * ref: fast_ep expand (fast_ep_kernels.cu:179-214). */
+int epsb_scatter_rows(const void* src, void* dst, const int32_t* map, int32_t div, int64_t n, int64_t row_bytes,
+                      void* stream);
+
+/* Segment copy: for p < n_seg, rows [src_off[p], +rows[p]) -> [dst_off[p], ...).
+ * ref: fast_ep arrange (fast_ep_kernels.cu:653-690). */
+int epsb_arrange_rows(const void* src, void* dst, const int32_t* src_off, const int32_t* rows, const int32_t* dst_off,
+                      int n_seg, int64_t max_rows, int64_t row_bytes, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * Reductions.  H % 8 == 0.
+ * -------------------------------------------------------------------------- */
+
+/* Reference-arithmetic local reduce: send[q,:] = sum_j bf16(w[scale_map[q],j]) *
+ * y[red_map[q,j],:] in bf16 multiply / bf16 accumulate, for q in the stage
+ * window of every source rank.
+ * ref: localReduce (src/scheduler/local_reducer.cu:103-211). stage -1 = all. */
+int epsb_local_reduce_ref(const void* y, const float* w_recv, const int32_t* scale_map, const int32_t* red_map,
+                          const int32_t* ret_incl, int k, int W, int S, int stage, int64_t max_rows, int64_t H,
+                          void* send, void* stream);
+
+/* Fast local reduce for the fused path: y rows are already weighted (fp32, in
+ * the down-GEMM epilogue); send[q,:] = bf16(sum_j float(y[red_map[q,j],:])),
+ * fp32 accumulation in slot order. */
+int epsb_local_reduce(const void* y, const int32_t* red_map, const int32_t* ret_incl, int k, int W, int S, int stage,
+                      int64_t max_rows, int64_t H, void* send, void* stream);
+
+/* Reference-arithmetic global reduce + zero-expert term:
+ * out[t,:] = (shared[t,:] +) sum_ep recv[glob_map[t,ep],:] in bf16 adds, then
+ * out += bf16(float(x[t,:]) * zero_scale[t]) when zero_scale != NULL.
+ * ref: globalReduce (src/scheduler/global_reducer.cu:126-208),
+ *      zeroReduce (src/scheduler/zero_reducer.cu:34-50). */
+int epsb_global_reduce_ref(const void* recv, const int32_t* glob_map, const void* shared, const void* x,
+                           const float* zero_scale, int T, int W, int64_t H, void* out, void* stream);
+
+/* Fused form: one fp32 accumulation, one bf16 rounding. */
+int epsb_global_reduce(const void* recv, const int32_t* glob_map, const void* shared, const void* x,
+                       const float* zero_scale, int T, int W, int64_t H, void* out, void* stream);
+
+/* fast_ep combine: out[t,:] = bf16(sum_j w[t,j]*row(mapping[t*k+j]) (+shared)),
+ * fp32 FMA accumulation; mapping >= 1000000 reads raw token mapping-1000000.
+ * ref: fast_ep reduce (fast_ep_kernels.cu:231-335). */
+int epsb_fastep_reduce(const void* rows, const void* raw, const void* shared, const float* w, const int32_t* mapping,
+                       int T, int k, int64_t H, void* out, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * SwiGLU (unfused, bf16 callers).  ref: silu_activate
+ * (src/executor/activations.cu:9-40,173-205; src/executor/bindings/silu_ops.cu:14-43).
+ * gate_up [rows, 2I] bf16 ([gate | up]) -> act [rows, I] bf16 over rows
+ * [exclusive_sum[0], exclusive_sum[num_experts]) (or all `rows` if NULL).
+ * -------------------------------------------------------------------------- */
+int epsb_silu_run(const void* gate_up, void* act, const int32_t* exclusive_sum, int num_experts, int64_t rows,
+                  int64_t inter_size, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * FP8 block-scaled grouped GEMM (tcgen05 + TMEM, persistent ragged-M scheduler).
+ * ref: GemmInterface::run (src/scheduler/gemm_executor_interface.cuh:3-29),
+ *      AokGroupedGemm::run (src/executor/aok_grouped_gemm.cu:22-37),
+ *      SM90_GROUPED_GEMM::Launch (src/gemm/aok_grouped_gemm/src/operations/
+ *      hopper_grouped_gemm_kernel.h:322-400).  The A_scales / weight_scales
+ *      slots of RunParams are the a_s / b_s arguments here.
+ *
+ * For local expert e, rows [excl[e], excl[e+1]) of A:
+ *   C[m,n] = sum_kb a_s[m,kb] * b_s[e, n/128, kb] * sum_{k in kb} A[m,k]*B[e,n,k]
+ * A   [max_rows, K] e4m3 row-major; a_s [max_rows, K/128] fp32 row-major
+ * B   [EL, N, K] e4m3 (K contiguous); b_s [EL, N/128, K/128] fp32
+ * excl [EL+1] int32 on the device (never read on the host)
+ * K % 128 == 0, N % 128 == 0.
+ *
+ * status: optional int32[4] device words; word 0 is set nonzero if a bounded
+ * device-side wait expired (the kernel then drains and exits instead of
+ * hanging).  Read it with epsb_gemm_status after synchronising.
+ *
+ * mode EPSB_GEMM_PLAIN : C [max_rows, N] bf16 = result.
+ * mode EPSB_GEMM_GATEUP: N = 2I, B rows are [gate(I) | up(I)] (activations.cu:19-20);
+ *      act = silu(gate)*up in fp32, requantised per row per 128 columns:
+ *      C is e4m3 [max_rows, I], c_s [max_rows, I/128] fp32.  I % 128 == 0.
+ * mode EPSB_GEMM_DOWN  : C [max_rows, N] bf16 = result * row_w[m] (fp32), the
+ *      top-k gate weight of GEMM row m; row_w NULL = 1.
+ * -------------------------------------------------------------------------- */
+#define EPSB_GEMM_PLAIN 0
+#define EPSB_GEMM_GATEUP 1
+#define EPSB_GEMM_DOWN 2
+int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
+                          const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
+                          float* c_s, const float* row_w, int32_t* status, void* stream);
+
+/* Gathers the per-GEMM-row gate weight: row_w[d] = w_recv[gemm_map[d]] for
+ * d < excl[EL] (w_recv is [R,k] flat, gemm_map holds row*k+slot). */
+int epsb_gather_row_weights(const float* w_recv, const int32_t* gemm_map, const int32_t* excl, int num_experts,
+                            int64_t max_rows, float* row_w, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EPS_B200_H_ */

@@ -1,0 +1,165 @@
+// extern "C" launchers around the REFERENCE's own arch-agnostic CUDA kernels.
+//
+// TEST INFRASTRUCTURE ONLY.  This file contains no reference code: it includes the reference's
+// headers from where they lie and calls the reference's launchers, so that the kernels the
+// reference ships can run on a B200 as a second witness for the CPU oracle and for this
+// repository's kernels.  oracle/build_ref.py compiles it together with the reference's .cu
+// files (in place, never copied) into oracle/_ref/libeps_ref.so.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include "src/executor/activations.cuh"
+#include "src/quant/fp8.cuh"
+#include "src/scheduler/comm_expander.cuh"
+#include "src/scheduler/gemm_expander.cuh"
+#include "src/scheduler/global_reducer.cuh"
+#include "src/scheduler/local_reducer.cuh"
+#include "src/scheduler/zero_reducer.cuh"
+
+using bf16 = __nv_bfloat16;
+
+extern "C" {
+
+int ref_sync() { return (int)cudaDeviceSynchronize(); }
+
+// scheduler/comm_expander_ver2.cu:174
+void ref_comm_plan(const int* idx, int* leading_ws, int* mapping, int* incl, int T, int k, int E, int S, int W) {
+  eps::ExpandForCommPlanKernelParams p{};
+  p.expert_indices = idx;
+  p.sorted_leading_experts = leading_ws;
+  p.expand_plan = eps::ExpandForCommPlan{mapping, incl};
+  p.num_tokens = T;
+  p.topk = k;
+  p.num_experts = E;
+  p.num_stages = S;
+  p.ep_world_size = W;
+  p.tile_states = nullptr;
+  eps::getExpandForCommPlan_ver2(p, 0);
+}
+
+// scheduler/gemm_expander_ver2.cu:180
+void ref_gemm_plan(int* ridx, const int* recv_incl, int* mapping, int* excl, int lo, int hi, int E, int S, int k,
+                   int W, long long max_tok) {
+  eps::ExpandForGemmPlanKernelParams p{};
+  p.expert_indices = ridx;
+  p.sorted_expert_indices = nullptr;
+  p.inclusive_sum = recv_incl;
+  p.expand_plan = eps::ExpandForGemmPlan{mapping, excl};
+  p.local_expert_begin = lo;
+  p.local_expert_end = hi;
+  p.num_experts = E;
+  p.num_stages = S;
+  p.topk = k;
+  p.ep_world_size = W;
+  p.max_num_tokens_per_gpu = max_tok;
+  eps::getExpandForGemmPlan_ver2(p, 0);
+}
+
+// scheduler/local_reducer_ver2.cu:471
+void ref_local_reduce_plan(const int* ridx, int* tail_ws, int* sorted_tail_ws, const int* recv_incl, int* red_map,
+                           int* scale_map, int* ret_incl, int* gemm_map, int* excl, int lo, int hi, int E, int S,
+                           int k, int W, long long max_tok, int num_global_tokens) {
+  eps::LocalReducePlanKernelParams p{};
+  p.expert_indices = ridx;
+  p.tailing_experts = tail_ws;
+  p.sorted_tailing_experts = sorted_tail_ws;
+  p.inclusive_sum = recv_incl;
+  p.mapping = nullptr;
+  p.reduce_plan = eps::LocalReducePlan{red_map, scale_map, ret_incl};
+  p.expand_plan = eps::ExpandForGemmPlan{gemm_map, excl};
+  p.local_expert_begin = lo;
+  p.local_expert_end = hi;
+  p.num_experts = E;
+  p.num_stages = S;
+  p.topk = k;
+  p.ep_world_size = W;
+  p.max_num_tokens_per_gpu = max_tok;
+  eps::getLocalReducePlan_ver2(p, 0, num_global_tokens);
+}
+
+// scheduler/global_reducer_ver2.cu:206
+void ref_global_reduce_plan(const int* idx, int* tail_ws, int* glob_map, int* coll_incl, int* send_map,
+                            int* send_incl, int T, int E, int S, int k, int W) {
+  eps::GlobalReducePlanKernelParams p{};
+  p.expert_indices = idx;
+  p.tailing_experts = tail_ws;
+  p.sorted_tailing_experts = nullptr;
+  p.reduce_plan = eps::GlobalReducePlan{glob_map, coll_incl};
+  p.expand_plan = eps::ExpandForCommPlan{send_map, send_incl};
+  p.num_tokens = T;
+  p.num_experts = E;
+  p.num_stages = S;
+  p.topk = k;
+  p.ep_world_size = W;
+  eps::getGlobalReducePlan_ver2(p, 0);
+}
+
+// scheduler/zero_reducer.cu:27,44
+void ref_zero_plan(const int* idx, const float* w, int T, int k, float* zero_scale) {
+  eps::ZeroReducePlanKernelParams<bf16, float> p{};
+  p.expert_indices = idx;
+  p.expert_scales = w;
+  p.num_local_tokens = T;
+  p.topk = k;
+  p.zero_reduce_plan.zero_reduce_scales = zero_scale;
+  eps::getZeroReducePlan(p, 0);
+}
+void ref_zero_reduce(float* zero_scale, int T, long long H, const void* x, void* out) {
+  eps::ZeroReduceKernelParams<bf16, bf16, float> p{};
+  p.zero_reduce_scales = zero_scale;
+  p.num_local_tokens = T;
+  p.hidden_size = H;
+  p.raw_input = (const bf16*)x;
+  p.output = (bf16*)out;
+  eps::zeroReduce(p, 0);
+}
+
+// scheduler/local_reducer.cu:193 (bf16 rows, fp32 gate weights)
+void ref_local_reduce(int* red_map, int* scale_map, int* ret_incl, int S, int k, int W, long long H, const void* y,
+                      void* send, const float* w_recv, long long hint, int stage) {
+  eps::LocalReduceKernelParams<bf16, float> p{};
+  p.reduce_plan = eps::LocalReducePlan{red_map, scale_map, ret_incl};
+  p.num_stages = S;
+  p.topk = k;
+  p.ep_world_size = W;
+  p.hidden_size = H;
+  p.src = (const bf16*)y;
+  p.dst = (bf16*)send;
+  p.expert_scales = w_recv;
+  p.num_tokens_hint = hint;
+  eps::localReduce(p, stage, 0);
+}
+
+// scheduler/global_reducer.cu:183
+void ref_global_reduce(int* glob_map, int T, int W, long long H, const void* recv, void* out, const void* shared) {
+  eps::GlobalReduceKernelParams<bf16> p{};
+  p.reduce_plan = eps::GlobalReducePlan{glob_map, nullptr};
+  p.num_tokens = T;
+  p.ep_world_size = W;
+  p.hidden_size = H;
+  p.src = (const bf16*)recv;
+  p.dst = (bf16*)out;
+  p.shared = (const bf16*)shared;
+  eps::globalReduce(p, 0);
+}
+
+// quant/fp8.cu:362 (dense form)
+void ref_quant_1x128(void* x, long long rows, long long cols, void* q, float* scales) {
+  eps::PerTokenGroupQuantFP8DenseParams<bf16> p{};
+  p.quanted = (eps::FP8_TYPE*)q;
+  p.origin = (bf16*)x;
+  p.scales = scales;
+  p.cols = cols;
+  p.group_size = 128;
+  p.num_tokens = rows;
+  p.dequant = false;
+  eps::per_token_group_quant_fp8<bf16, eps::PerTokenGroupQuantFP8DenseParams>(p, 0);
+}
+
+// executor/activations.cu (ragged form)
+void ref_silu(const void* gate_up, void* act, const int* excl, int num_experts, int inter_x2, int hint) {
+  eps::silu_activate<bf16>((const bf16*)gate_up, (bf16*)act, excl, num_experts, inter_x2, hint, 0);
+}
+
+}  // extern "C"

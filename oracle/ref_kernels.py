@@ -1,0 +1,134 @@
+"""ctypes face of oracle/_ref/libeps_ref.so: the REFERENCE's own kernels, run on the GPU.
+
+TEST INFRASTRUCTURE ONLY (second witness for the oracle and generator of tests/golden fixtures).
+All arguments are torch CUDA tensors; every call synchronises before returning.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(_HERE, "_ref", "libeps_ref.so")
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(LIB)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(LIB)
+    return _lib
+
+
+def _p(t):
+    return ctypes.c_void_p(None if t is None else t.data_ptr())
+
+
+def _sync():
+    rc = lib().ref_sync()
+    if rc != 0:
+        raise RuntimeError(f"reference kernel failed: cudaError {rc}")
+
+
+def _i32(n, dev, fill=None):
+    t = torch.empty((max(int(n), 1),), dtype=torch.int32, device=dev)
+    if fill is not None:
+        t.fill_(fill)
+    return t
+
+
+def comm_plan(idx, E, W, S):
+    T, k = idx.shape
+    dev = idx.device
+    lead = _i32(T * W, dev)
+    mapping = _i32(T * W, dev, -1)
+    incl = _i32(W * S, dev, 0)
+    lib().ref_comm_plan(_p(idx), _p(lead), _p(mapping), _p(incl), T, k, E, S, W)
+    _sync()
+    return mapping, incl
+
+
+def gemm_plan(ridx, recv_incl, k, lo, hi, E, W, S, max_tok):
+    dev = ridx.device
+    R = ridx.shape[0]
+    mapping = _i32(R * k, dev, -1)
+    excl = _i32(hi - lo + 1, dev, 0)
+    lib().ref_gemm_plan(_p(ridx), _p(recv_incl), _p(mapping), _p(excl), lo, hi, E, S, k, W,
+                        ctypes.c_longlong(max_tok))
+    _sync()
+    return excl, mapping
+
+
+def local_reduce_plan(ridx, recv_incl, gemm_map, excl, k, lo, hi, E, W, S, max_tok, num_global_tokens):
+    dev = ridx.device
+    R = ridx.shape[0]
+    tail, stail = _i32(R, dev), _i32(R, dev)
+    red_map, scale_map, ret_incl = _i32(R * k, dev, -1), _i32(R, dev, -1), _i32(W * S, dev, 0)
+    lib().ref_local_reduce_plan(_p(ridx), _p(tail), _p(stail), _p(recv_incl), _p(red_map), _p(scale_map),
+                                _p(ret_incl), _p(gemm_map), _p(excl), lo, hi, E, S, k, W,
+                                ctypes.c_longlong(max_tok), num_global_tokens)
+    _sync()
+    return scale_map, red_map, ret_incl
+
+
+def global_reduce_plan(idx, send_map, send_incl, E, W, S):
+    T, k = idx.shape
+    dev = idx.device
+    tail = _i32(T * W, dev)
+    glob, coll = _i32(T * W, dev, -1), _i32(W * S, dev, 0)
+    lib().ref_global_reduce_plan(_p(idx), _p(tail), _p(glob), _p(coll), _p(send_map), _p(send_incl), T, E, S, k, W)
+    _sync()
+    return glob, coll
+
+
+def zero_plan(idx, w):
+    T, k = idx.shape
+    z = torch.zeros((max(T, 1),), dtype=torch.float32, device=idx.device)
+    lib().ref_zero_plan(_p(idx), _p(w), T, k, _p(z))
+    _sync()
+    return z
+
+
+def zero_reduce(zero_scale, x, out):
+    T, H = x.shape
+    lib().ref_zero_reduce(_p(zero_scale), T, ctypes.c_longlong(H), _p(x), _p(out))
+    _sync()
+    return out
+
+
+def local_reduce(red_map, scale_map, ret_incl, S, k, W, y, send, w_recv, hint, stage):
+    H = y.shape[1]
+    lib().ref_local_reduce(_p(red_map), _p(scale_map), _p(ret_incl), S, k, W, ctypes.c_longlong(H), _p(y), _p(send),
+                           _p(w_recv), ctypes.c_longlong(hint), stage)
+    _sync()
+    return send
+
+
+def global_reduce(glob_map, W, recv, out, shared=None):
+    T, H = out.shape
+    lib().ref_global_reduce(_p(glob_map), T, W, ctypes.c_longlong(H), _p(recv), _p(out), _p(shared))
+    _sync()
+    return out
+
+
+def quant_1x128(x):
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
+    lib().ref_quant_1x128(_p(x), ctypes.c_longlong(rows), ctypes.c_longlong(cols), _p(q), _p(s))
+    _sync()
+    return q, s
+
+
+def silu(gate_up, excl, num_experts, hint):
+    rows, two_i = gate_up.shape
+    act = torch.zeros((rows, two_i // 2), dtype=torch.bfloat16, device=gate_up.device)
+    lib().ref_silu(_p(gate_up), _p(act), _p(excl), num_experts, two_i, hint)
+    _sync()
+    return act

@@ -1,0 +1,102 @@
+"""Records golden vectors from the REFERENCE's own kernels (oracle/_ref/libeps_ref.so) on a GPU.
+
+Run on a B200:  python tests/golden/make_ref_fixtures.py gpurun_out/golden
+then copy the .npz it writes into tests/golden/.  The CPU test tests/test_oracle_golden.py checks
+the oracle against these files, which is the oracle's parity pin.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from helpers import random_routing, simulate_eps  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+from oracle import ref_kernels as ref  # noqa: E402
+
+# W, S, E, k, T, n_zero, max_tok   (sizes keep the reference kernels' shared memory under the limit)
+PLAN_CASES = [
+    (1, 1, 8, 2, 37, 0, 64),
+    (1, 2, 16, 4, 256, 0, 256),
+    (2, 2, 16, 4, 300, 2, 512),
+    (4, 2, 32, 8, 129, 4, 256),
+    (8, 4, 256, 8, 128, 0, 128),
+    (8, 1, 64, 6, 520, 8, 1024),
+]
+
+
+def main(out_dir):
+    os.makedirs(out_dir, exist_ok=True)
+    dev = torch.device("cuda:0")
+    blob = {}
+    for ci, (W, S, E, k, T, nz, max_tok) in enumerate(PLAN_CASES):
+        rng = np.random.default_rng(4242 + ci)
+        Ts = [max(1, T - 5 * r) for r in range(W)]
+        routing = [random_routing(rng, Ts[r], k, E, nz) for r in range(W)]
+        ranks = simulate_eps(orc, [rt[0] for rt in routing], E, W, S, max_tok)
+        EL = E // W
+        for r in range(W):
+            idx, w = routing[r]
+            d_idx = torch.from_numpy(idx).to(dev)
+            send_map, send_incl = ref.comm_plan(d_idx, E, W, S)
+            glob, coll = ref.global_reduce_plan(d_idx, send_map, send_incl, E, W, S)
+            zero = ref.zero_plan(d_idx, torch.from_numpy(w).to(dev))
+            n = int(send_incl[-1].item())
+            pre = f"c{ci}_r{r}_"
+            blob[pre + "idx"] = idx
+            blob[pre + "w"] = w
+            blob[pre + "send_map"] = send_map.cpu().numpy()[:n]
+            blob[pre + "send_incl"] = send_incl.cpu().numpy()
+            blob[pre + "glob_map"] = glob.cpu().numpy()[:Ts[r] * W].reshape(Ts[r], W)
+            blob[pre + "coll_incl"] = coll.cpu().numpy()
+            blob[pre + "zero_scale"] = zero.cpu().numpy()[:Ts[r]]
+            # expert side: inputs are the rows this rank receives (built with the oracle's dispatch, which the
+            # source-side fixtures above pin)
+            rk = ranks[r]
+            R = rk["R"]
+            if R == 0:
+                continue
+            d_ridx = torch.from_numpy(rk["ridx"]).to(dev)
+            d_recv = torch.from_numpy(rk["recv_incl"]).to(dev)
+            excl, gmap = ref.gemm_plan(d_ridx, d_recv, k, r * EL, (r + 1) * EL, E, W, S, max_tok)
+            D = int(excl[-1].item())
+            for ngt in (sum(Ts), 16):  # the threaded kernel and the one-thread "decode" kernel
+                if ngt * k <= 4096 and R > 4096:
+                    continue
+                scale_map, red_map, ret_incl = ref.local_reduce_plan(d_ridx, d_recv, gmap, excl, k, r * EL,
+                                                                     (r + 1) * EL, E, W, S, max_tok, ngt)
+                tag = "dec_" if ngt * k <= 4096 else "thr_"
+                blob[pre + tag + "scale_map"] = scale_map.cpu().numpy()[:R]
+                blob[pre + tag + "red_map"] = red_map.cpu().numpy()[:R * k].reshape(R, k)
+                blob[pre + tag + "ret_incl"] = ret_incl.cpu().numpy()
+            blob[pre + "ridx"] = rk["ridx"]
+            blob[pre + "recv_incl"] = rk["recv_incl"]
+            blob[pre + "excl"] = excl.cpu().numpy()
+            blob[pre + "gemm_map"] = gmap.cpu().numpy()[:D]
+    blob["plan_cases"] = np.array(PLAN_CASES, dtype=np.int64)
+    np.savez_compressed(os.path.join(out_dir, "ref_plans.npz"), **blob)
+
+    # quantisation: the reference kernel uses an approximate divide for the scale; record codes and scales
+    g = torch.Generator().manual_seed(99)
+    x = torch.randn((64, 1024), generator=g).to(torch.bfloat16)
+    x[3, 128:256] = 0
+    x[5] *= 1e-5
+    q, s = ref.quant_1x128(x.to(dev))
+    np.savez_compressed(os.path.join(out_dir, "ref_quant.npz"), x=x.view(torch.int16).numpy().view(np.uint16),
+                        q=q.cpu().numpy(), s=s.cpu().numpy())
+
+    # SwiGLU
+    gu = torch.randn((40, 2 * 1408), generator=g).to(torch.bfloat16)
+    excl = torch.tensor([0, 40], dtype=torch.int32)
+    act = ref.silu(gu.to(dev), excl.to(dev), 1, 40)
+    np.savez_compressed(os.path.join(out_dir, "ref_silu.npz"), gu=gu.view(torch.int16).numpy().view(np.uint16),
+                        act=act.cpu().view(torch.int16).numpy().view(np.uint16))
+    print("wrote fixtures to", out_dir, {k: v.shape for k, v in list(blob.items())[:4]})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")

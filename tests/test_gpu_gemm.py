@@ -1,0 +1,114 @@
+"""tcgen05 FP8 block-scaled grouped GEMM against the fp32 dequantised oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _make(oracle, rng, rows_per_expert, N, K, pad_rows=5):
+    E = len(rows_per_expert)
+    excl = np.zeros(E + 1, dtype=np.int32)
+    excl[1:] = np.cumsum(rows_per_expert)
+    D = int(excl[-1])
+    max_rows = D + pad_rows
+    a = oracle.bf16_bits(rng.standard_normal((max_rows, K)).astype(np.float32))
+    A, a_s = oracle.quant_1x128(a)
+    w = (rng.standard_normal((E, N, K)) * 0.02).astype(np.float32)
+    w = oracle.bf16_to_f32(oracle.bf16_bits(w))
+    B, b_s = oracle.quant_block128(w)
+    return excl, D, max_rows, A, a_s, B, b_s
+
+
+def _check_status(status):
+    st = status.cpu().tolist()
+    assert st[0] == 0, f"bounded wait expired in the GEMM kernel: code {st[0]} on CTA {st[1]}"
+
+
+GEMM_CASES = [
+    ([128], 256, 128),
+    ([1], 256, 256),
+    ([130, 0, 7], 256, 512),
+    ([64] * 16, 2048, 1408 - 1408 % 128),
+    ([300, 5, 0, 129, 128, 1, 77, 256], 512, 2048),
+]
+
+
+@pytest.mark.parametrize("rows,N,K", GEMM_CASES)
+def test_gemm_plain(cuda, oracle, rows, N, K):
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(N + K + len(rows))
+    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, rows, N, K)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    C = torch.full((max_rows, N), 7.0, dtype=torch.bfloat16, device=cuda)
+    ops.grouped_gemm_fp8(ops.GEMM_PLAIN, _dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda),
+                         _dev(excl, cuda), out=C, status=status)
+    torch.cuda.synchronize()
+    _check_status(status)
+    want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl)
+    got = C.float().cpu().numpy()
+    rms = np.sqrt(np.mean(want[:D] ** 2)) if D else 1.0
+    # bf16 output rounding (2^-9 relative) + fp32 summation-order differences; tolerance stated vs RMS
+    assert np.max(np.abs(got[:D] - want[:D])) <= 2e-2 * rms
+    assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
+    assert np.all(got[D:] == 7.0), "rows outside every expert must not be written"
+
+
+@pytest.mark.parametrize("rows,I,K", [([128], 128, 128), ([5, 140], 256, 512), ([64] * 16, 1408 - 1408 % 128, 2048),
+                                       ([200, 0, 3, 131], 2048, 1024)])
+def test_gemm_gateup_swiglu_requant(cuda, oracle, rows, I, K):
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(I + K)
+    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, rows, 2 * I, K)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    q = torch.full((max_rows, I), 0xAA, dtype=torch.uint8, device=cuda)
+    s = torch.full((max_rows, I // 128), -1.0, dtype=torch.float32, device=cuda)
+    ops.grouped_gemm_fp8(ops.GEMM_GATEUP, _dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda),
+                         _dev(excl, cuda), out=q, out_scales=s, status=status)
+    torch.cuda.synchronize()
+    _check_status(status)
+    act = oracle.swiglu(oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl))
+    gq, gs = q.cpu().numpy(), s.cpu().numpy()
+    assert np.all(gq[D:] == 0xAA) and np.all(gs[D:] == -1.0)
+    deq = oracle.e4m3_table()[gq[:D]] * np.repeat(gs[:D], 128, axis=1)
+    rms = np.sqrt(np.mean(act[:D] ** 2))
+    # the requantised activation carries half an e4m3 ulp (2^-4 of the group amax) of error by design
+    amax = np.abs(act[:D]).reshape(D, I // 128, 128).max(-1)
+    assert np.all(np.abs(gs[:D] - amax / 448.0) <= np.abs(amax / 448.0) * 1e-3 + 1e-12)
+    bound = np.repeat(amax, 128, axis=1) * (2.0 ** -4) * 1.05 + 1e-3 * rms
+    assert np.all(np.abs(deq - act[:D]) <= bound)
+
+
+@pytest.mark.parametrize("rows,N,K", [([128], 256, 128), ([9, 250, 0, 40], 512, 1408 - 1408 % 128)])
+def test_gemm_down_weighted(cuda, oracle, rows, N, K):
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(N * 3 + K)
+    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, rows, N, K)
+    row_w = rng.random(max_rows).astype(np.float32)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    C = ops.grouped_gemm_fp8(ops.GEMM_DOWN, _dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda),
+                             _dev(excl, cuda), row_w=_dev(row_w, cuda), status=status)
+    torch.cuda.synchronize()
+    _check_status(status)
+    want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl) * row_w[:, None]
+    got = C.float().cpu().numpy()
+    rms = np.sqrt(np.mean(want[:D] ** 2))
+    assert np.max(np.abs(got[:D] - want[:D])) <= 2e-2 * rms
+    assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
+
+
+def test_gemm_errors(cuda):
+    from eps_b200 import ops
+    from eps_b200._lib import EpsError
+
+    A = torch.zeros((4, 100), dtype=torch.uint8, device=cuda)
+    with pytest.raises(EpsError):
+        ops.grouped_gemm_fp8(ops.GEMM_PLAIN, A, torch.zeros((4, 1), device=cuda), torch.zeros((1, 128, 100), dtype=torch.uint8, device=cuda),
+                             torch.zeros((1, 1, 1), device=cuda), torch.zeros(2, dtype=torch.int32, device=cuda))

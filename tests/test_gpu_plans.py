@@ -1,0 +1,123 @@
+"""CUDA plan kernels against the CPU oracle: every index array bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import random_routing, simulate_eps
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # W, S, E, k, T, n_zero, max_tok
+    (1, 1, 8, 2, 1, 0, 1),
+    (1, 1, 8, 2, 3, 0, 3),
+    (1, 1, 16, 4, 17, 0, 17),
+    (1, 2, 16, 4, 256, 0, 256),
+    (2, 1, 8, 3, 40, 2, 64),
+    (2, 2, 16, 4, 300, 0, 512),
+    (4, 2, 32, 8, 129, 4, 256),
+    (8, 4, 256, 8, 128, 0, 128),
+    (8, 1, 256, 8, 520, 0, 4096),
+    (8, 2, 512, 12, 96, 256, 128),
+    (1, 1, 128, 8, 2100, 0, 8192),
+]
+
+
+def _dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+@pytest.mark.parametrize("W,S,E,k,T,nz,max_tok", CASES)
+def test_eps_plans_bit_exact(cuda, oracle, W, S, E, k, T, nz, max_tok):
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(W * 1000 + T)
+    Ts = [max(0, T - 5 * r) for r in range(W)]
+    routing = [random_routing(rng, Ts[r], k, E, nz) for r in range(W)]
+    ranks = simulate_eps(oracle, [rt[0] for rt in routing], E, W, S, max_tok)
+    EL = E // W
+    for r in range(W):
+        rk = ranks[r]
+        idx, w = routing[r]
+        if Ts[r] == 0:
+            continue
+        send_map, send_incl, glob_map, coll_incl, zero = ops.source_plans(_dev(idx, cuda), _dev(w, cuda), E, W, S)
+        torch.cuda.synchronize()
+        n = int(rk["send_incl"][-1])
+        assert np.array_equal(send_incl.cpu().numpy(), rk["send_incl"])
+        assert np.array_equal(send_map.cpu().numpy()[:n], rk["send_map"])
+        assert np.array_equal(glob_map.cpu().numpy()[:Ts[r] * W].reshape(Ts[r], W), rk["glob_map"])
+        assert np.array_equal(coll_incl.cpu().numpy(), rk["coll_incl"])
+        assert np.array_equal(zero.cpu().numpy()[:Ts[r]], oracle.zero_plan(idx, w))
+    gathered = np.stack([ranks[r]["send_incl"] for r in range(W)], 0)
+    for r in range(W):
+        rk = ranks[r]
+        total = torch.full((1,), -1, dtype=torch.int32, device=cuda)
+        recv_incl, remote = ops.recv_plan(_dev(gathered, cuda), r, W, S, total_rows=total)
+        torch.cuda.synchronize()
+        assert np.array_equal(recv_incl.cpu().numpy(), rk["recv_incl"])
+        assert np.array_equal(remote.cpu().numpy(), rk["remote"])
+        assert total.item() == rk["R"]
+        R = rk["R"]
+        max_rows = max(R, 1) + 3
+        ridx = np.full((max_rows, k), -7, dtype=np.int32)
+        ridx[:R] = rk["ridx"]
+        excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl = ops.expert_plans(
+            _dev(ridx, cuda), recv_incl, k, r * EL, (r + 1) * EL, W, S, max_tok, max_rows)
+        torch.cuda.synchronize()
+        D = int(rk["excl"][-1])
+        assert np.array_equal(excl.cpu().numpy(), rk["excl"])
+        assert np.array_equal(gemm_map.cpu().numpy()[:D], rk["gemm_map"])
+        assert np.array_equal(scale_map.cpu().numpy()[:R], rk["scale_map"])
+        assert np.array_equal(red_map.cpu().numpy()[:R * k].reshape(R, k), rk["red_map"])
+        assert np.array_equal(ret_incl.cpu().numpy(), rk["ret_incl"])
+        inv = inv_gemm.cpu().numpy()[:R * k]
+        ok = inv < R * k
+        assert ok.sum() == D and np.array_equal(gemm_map.cpu().numpy()[inv[ok]], np.nonzero(ok)[0])
+
+
+def test_source_plans_empty_tokens(cuda):
+    from eps_b200 import ops
+
+    idx = torch.empty((0, 4), dtype=torch.int32, device=cuda)
+    w = torch.empty((0, 4), dtype=torch.float32, device=cuda)
+    _, send_incl, _, coll_incl, _ = ops.source_plans(idx, w, 16, 2, 2)
+    assert send_incl.cpu().tolist() == [0, 0, 0, 0] and coll_incl.cpu().tolist() == [0, 0, 0, 0]
+
+
+def test_plan_errors(cuda):
+    from eps_b200 import ops
+    from eps_b200._lib import EpsError
+
+    idx = torch.zeros((4, 2), dtype=torch.int32, device=cuda)
+    w = torch.ones((4, 2), dtype=torch.float32, device=cuda)
+    with pytest.raises(EpsError, match="Invalid num_stages"):
+        ops.source_plans(idx, w, 12, 2, 4)
+    with pytest.raises(EpsError):
+        ops.source_plans(idx, w, 4096, 2, 1)
+
+
+@pytest.mark.parametrize("E,k,T,nz", [(8, 2, 5, 0), (32, 4, 100, 0), (256, 8, 4096, 0), (512, 12, 700, 256), (24, 3, 64, 5)])
+def test_fastep_expand_plan_bit_exact(cuda, oracle, E, k, T, nz):
+    from eps_b200 import ops
+
+    idx, _ = random_routing(np.random.default_rng(E + T), T, k, E, nz)
+    excl, mapping = ops.fastep_expand_plan(_dev(idx, cuda), E)
+    torch.cuda.synchronize()
+    rex, rmap = oracle.fastep_expand_plan(idx, E)
+    assert np.array_equal(excl.cpu().numpy(), rex)
+    assert np.array_equal(mapping.cpu().numpy()[:T * k], rmap)
+
+
+@pytest.mark.parametrize("W,E,k,T", [(1, 8, 2, 19), (2, 8, 3, 40), (4, 32, 4, 25), (8, 256, 8, 300)])
+def test_fastep_plan_bit_exact(cuda, oracle, W, E, k, T):
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(9 * W)
+    ag = np.stack([oracle.fastep_expand_plan(random_routing(rng, T + r, k, E)[0], E)[0] for r in range(W)], 0)
+    for d in range(W):
+        got = ops.fastep_plan(_dev(ag, cuda), d, W, E)
+        torch.cuda.synchronize()
+        want = oracle.fastep_plan(ag, d, W, E)
+        for g, w_ in zip(got, want):
+            assert np.array_equal(g.cpu().numpy(), w_)
