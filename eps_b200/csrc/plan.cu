@@ -6,7 +6,7 @@
 // reference's visiting order ("virtual order"), cut into one contiguous range
 // per warp, counted per warp with warp-match votes (no atomics), scanned over
 // warps and over buckets, and emitted by rank.  The outputs are bit-identical
-// to the reference's for any input whose top-k ids are distinct per token.
+// to the reference's, including for inputs that repeat an expert id inside a token.
 #include "common.cuh"
 
 namespace epsb {
@@ -87,21 +87,22 @@ template <class P>
 __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned lt_mask = (1u << lane) - 1u;
-  const int chunk = ((n_pos + kPlanThreads - 1) / kPlanThreads) * 32;
-  const int p_begin = min(n_pos, warp * chunk), p_end = min(n_pos, p_begin + chunk);
+  // Items (position, slot) are numbered position-major; a warp owns a contiguous range of items and
+  // visits it 32 at a time, so the lane order inside a step is the visiting order.
   const int J = p.slots();
+  const int n_items = n_pos * J;
+  const int chunk = ((n_items + kPlanThreads - 1) / kPlanThreads) * 32;
+  const int i_begin = min(n_items, warp * chunk), i_end = min(n_items, i_begin + chunk);
   for (int i = threadIdx.x; i < kPlanWarps * B; i += kPlanThreads) s.rows[i] = 0;
   __syncthreads();
   int32_t* my_row = s.rows + warp * B;
-  for (int p0 = p_begin; p0 < p_end; p0 += 32) {
-    const int pos = p0 + lane;
-    const bool live = pos < p_end;
-    for (int j = 0; j < J; j++) {
-      const int key = live ? p.key(pos, j) : -1;
-      const unsigned m = __match_any_sync(0xffffffffu, key);
-      if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
-      __syncwarp();
-    }
+  for (int i0 = i_begin; i0 < i_end; i0 += 32) {
+    const int i = i0 + lane;
+    const bool live = i < i_end;
+    const int key = live ? p.key(i / J, i % J) : -1;
+    const unsigned m = __match_any_sync(0xffffffffu, key);
+    if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+    __syncwarp();
   }
   __syncthreads();
   for (int b = threadIdx.x; b < B; b += kPlanThreads) {
@@ -121,21 +122,20 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
     if (threadIdx.x < B) s.base[threadIdx.x] = inc - v;
   }
   __syncthreads();
-  for (int p0 = p_begin; p0 < p_end; p0 += 32) {
-    const int pos = p0 + lane;
-    const bool live = pos < p_end;
-    for (int j = 0; j < J; j++) {
-      const int key = live ? p.key(pos, j) : -1;
-      const unsigned m = __match_any_sync(0xffffffffu, key);
-      int mine = 0;
-      if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
-      __syncwarp();
-      if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
-      __syncwarp();
-      if (live) {
-        if (key >= 0) p.emit(pos, j, mine);
-        else p.skip(pos, j);
-      }
+  for (int i0 = i_begin; i0 < i_end; i0 += 32) {
+    const int i = i0 + lane;
+    const bool live = i < i_end;
+    const int pos = i / J, j = i % J;
+    const int key = live ? p.key(pos, j) : -1;
+    const unsigned m = __match_any_sync(0xffffffffu, key);
+    int mine = 0;
+    if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
+    __syncwarp();
+    if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+    __syncwarp();
+    if (live) {
+      if (key >= 0) p.emit(pos, j, mine);
+      else p.skip(pos, j);
     }
   }
   __syncthreads();

@@ -33,9 +33,11 @@ _FP8 = (torch.uint8, torch.float8_e4m3fn)
 # ------------------------------------------------------------------ quantisation
 
 
-def per_token_group_quant_fp8(x, exclusive_sum=None, num_experts=0, div_mode=0, out=None, out_scales=None):
+def per_token_group_quant_fp8(x, exclusive_sum=None, num_experts=0, div_mode=1, out=None, out_scales=None):
     """x [rows, cols] bf16 -> (codes uint8 [rows, cols], scales fp32 [rows, cols/128]).
 
+    div_mode 1 (default) computes the scale exactly like the reference kernel (div.full.f32, which on
+    B200 equals amax * fl(1/448)); div_mode 0 uses the IEEE quotient amax/448.
     With `exclusive_sum` only rows [exclusive_sum[0], exclusive_sum[num_experts]) are written
     (reference PerTokenGroupQuantFP8Params, src/quant/fp8.cuh:43-57)."""
     _check(x, "x", torch.bfloat16, 2)

@@ -13,8 +13,8 @@
  * Parity pin: the reference ships no tests, golden vectors or fixtures for this
  * path.  The pin is the reference's own arch-agnostic kernels compiled from its
  * sources (oracle/ref_harness.cu -> oracle/_ref/) and run on a B200; fixtures
- * recorded from that run live in tests/golden/.  One deliberate deviation from
- * the reference kernel is stated at orc_quant_1x128.
+ * recorded from that run live in tests/golden/ and tests/test_oracle_golden.py
+ * checks this file against them.
  */
 #include <math.h>
 #include <stdint.h>
@@ -91,13 +91,25 @@ void orc_e4m3_table(float* out256) {
  * the NaN operand, so every code of that group is 0x7E (+448) and dequantises to
  * 448*0 = 0.  C fminf/fmaxf have the same NaN rule as the CUDA ones.
  *
- * mode 0 (the contract of the FP8 layer, "amax/448"): IEEE division.
- * mode 1: the reference kernel's `div.full.f32`, which is an approximate
- * hardware divide (<= 2 ulp) that no CPU can restate from its definition; it is
- * modelled here as the correctly rounded quotient and the GPU tests measure how
- * often the real instruction differs.
+ * div_mode 1 (default of the product, what the reference kernel computes):
+ *   scale = div.full.f32(amax, 448) (fp8.cu:272-275).  PTX defines div.full only as
+ *   "approximate, <= 2 ulp", but on B200 it was compared with amax * fl(1/448)
+ *   over every positive float and the two agree bit for bit (2 139 095 040 of
+ *   2 139 095 040 inputs), so that product is what is restated here; the golden
+ *   vectors recorded from the reference kernel (tests/golden/ref_quant.npz) pin it.
+ *   It differs from the IEEE quotient by 1 ulp on ~59 % of scales.
+ * div_mode 0: scale = amax / 448 with IEEE division.
  */
-void orc_quant_1x128(const uint16_t* x_bf16, int64_t rows, int64_t cols, uint8_t* q, float* scales) {
+static inline float orc_scale_of_amax(float amax, int div_mode) {
+  if (div_mode == 1) {
+    const volatile float rcp = 1.0f / 448.0f; /* correctly rounded reciprocal, then one rounded product */
+    return amax * rcp;
+  }
+  return amax / 448.0f;
+}
+
+void orc_quant_1x128_mode(const uint16_t* x_bf16, int64_t rows, int64_t cols, uint8_t* q, float* scales,
+                          int div_mode) {
   const int64_t groups = cols / 128;
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < rows; r++) {
@@ -105,7 +117,7 @@ void orc_quant_1x128(const uint16_t* x_bf16, int64_t rows, int64_t cols, uint8_t
       const uint16_t* src = x_bf16 + r * cols + g * 128;
       float amax = 0.0f;
       for (int k = 0; k < 128; k++) amax = fmaxf(amax, fabsf(orc_bf16_to_f32(src[k])));
-      float scale = amax / 448.0f;
+      float scale = orc_scale_of_amax(amax, div_mode);
       scales[r * groups + g] = scale;
       float inv = 1.0f / scale;
       for (int k = 0; k < 128; k++) {
@@ -115,6 +127,10 @@ void orc_quant_1x128(const uint16_t* x_bf16, int64_t rows, int64_t cols, uint8_t
       }
     }
   }
+}
+
+void orc_quant_1x128(const uint16_t* x_bf16, int64_t rows, int64_t cols, uint8_t* q, float* scales) {
+  orc_quant_1x128_mode(x_bf16, rows, cols, q, scales, 0);
 }
 
 /* quant/fp8.cu:299-330: x = float(code) * scale, rounded to bf16. */

@@ -92,12 +92,13 @@ def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
 
 # ------------------------------------------------------------------ quant
 
-def quant_1x128(x_bits: np.ndarray):
+def quant_1x128(x_bits: np.ndarray, div_mode: int = 0):
+    """div_mode 0: scale = amax/448 (IEEE); 1: the reference kernel's div.full.f32 (= amax * fl(1/448))."""
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
     rows, cols = x_bits.shape
     q = np.empty((rows, cols), dtype=np.uint8)
     s = np.empty((rows, cols // 128), dtype=np.float32)
-    lib().orc_quant_1x128(_p(x_bits), _L(rows), _L(cols), _p(q), _p(s))
+    lib().orc_quant_1x128_mode(_p(x_bits), _L(rows), _L(cols), _p(q), _p(s), int(div_mode))
     return q, s
 
 

@@ -10,8 +10,9 @@ def _bits(t):
     return t.view(torch.int16).cpu().numpy().view(np.uint16)
 
 
+@pytest.mark.parametrize("div_mode", [0, 1])
 @pytest.mark.parametrize("rows,cols", [(1, 128), (3, 256), (17, 2048), (256, 7168), (1000, 1408 - 1408 % 128), (5, 6144)])
-def test_quant_1x128_bit_exact(cuda, oracle, rows, cols):
+def test_quant_1x128_bit_exact(cuda, oracle, rows, cols, div_mode):
     from eps_b200 import ops
 
     g = torch.Generator().manual_seed(rows * 131 + cols)
@@ -20,9 +21,9 @@ def test_quant_1x128_bit_exact(cuda, oracle, rows, cols):
     if rows > 2:
         x[2, 5] = 3e4  # outlier
         x[1] *= 1e-6   # tiny values (subnormal codes)
-    q, s = ops.per_token_group_quant_fp8(x.to(cuda))
+    q, s = ops.per_token_group_quant_fp8(x.to(cuda), div_mode=div_mode)
     torch.cuda.synchronize()
-    rq, rs = oracle.quant_1x128(_bits(x))
+    rq, rs = oracle.quant_1x128(_bits(x), div_mode=div_mode)
     assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
     assert np.array_equal(q.cpu().numpy(), rq)
 
@@ -48,7 +49,7 @@ def test_quant_ragged_window(cuda, oracle):
     s = torch.full((40, 3), -1.0, dtype=torch.float32, device=cuda)
     ops.per_token_group_quant_fp8(x.to(cuda), exclusive_sum=excl.to(cuda), num_experts=3, out=q, out_scales=s)
     torch.cuda.synchronize()
-    rq, rs = oracle.quant_1x128(_bits(x))
+    rq, rs = oracle.quant_1x128(_bits(x), div_mode=1)
     qc, sc = q.cpu().numpy(), s.cpu().numpy()
     assert np.array_equal(qc[7:31], rq[7:31]) and np.array_equal(sc[7:31], rs[7:31])
     assert np.all(qc[:7] == 0xAA) and np.all(qc[31:] == 0xAA) and np.all(sc[:7] == -1) and np.all(sc[31:] == -1)
@@ -93,13 +94,13 @@ def test_quant_full_size_properties(cuda):
     from eps_b200 import ops
 
     x = torch.randn((4096, 7168), device=cuda, dtype=torch.bfloat16)
-    q, s = ops.per_token_group_quant_fp8(x)
+    q, s = ops.per_token_group_quant_fp8(x, div_mode=0)
     d = ops.per_token_group_dequant_fp8(q, s)
     amax = x.float().view(4096, 56, 128).abs().amax(-1)
     assert torch.equal(s, amax / 448.0)
     err = (d.float() - x.float()).view(4096, 56, 128).abs().amax(-1)
     assert bool((err <= amax * 2.0 ** -4 + amax * 2.0 ** -8).all())
-    q2, s2 = ops.per_token_group_quant_fp8(d)
+    q2, s2 = ops.per_token_group_quant_fp8(d, div_mode=0)
     # re-quantising the dequantised rows reproduces the codes wherever bf16 rounding kept the amax
     same = (s2 == s)
     assert same.float().mean().item() > 0.5
