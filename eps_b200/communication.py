@@ -1,0 +1,101 @@
+"""Expert-parallel communicator: the transport under Scheduler and fast_ep.AllToAll.
+
+Mirrors the surface of the reference's MscclppCommunicator (python/eps/communication/__init__.py:35-71,
+src/communication/msccl_comm.cuh:14): create from a unique id + (rank, world, ranks_per_node), barrier,
+rank/world queries.  The reference moves bytes with mscclpp SM-copy kernels over CUDA-IPC arenas; here
+the variable-size all-to-all is one grouped NCCL send/recv per call over NVLink/NVSwitch (gloo on CPU for
+tests), launched through torch.distributed.  A world of one never touches a process group.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class CommunicatorParams:
+    rank: int
+    ep_world_size: int
+    num_ranks_per_node: int
+
+
+class Communicator:
+    """One expert-parallel group.  `group` is a torch.distributed process group (None = default group)."""
+
+    def __init__(self, unique_id=None, p: CommunicatorParams | None = None, group=None):
+        if p is None:
+            if dist.is_available() and dist.is_initialized():
+                p = CommunicatorParams(dist.get_rank(group), dist.get_world_size(group), dist.get_world_size(group))
+            else:
+                p = CommunicatorParams(0, 1, 1)
+        self.rank = int(p.rank)
+        self.world = int(p.ep_world_size)
+        self.num_ranks_per_node = int(p.num_ranks_per_node)
+        self.group = group
+        if self.world > 1:
+            if not dist.is_initialized():
+                raise RuntimeError("ep_world_size > 1 needs an initialised torch.distributed process group")
+            if dist.get_world_size(group) != self.world or dist.get_rank(group) != self.rank:
+                raise RuntimeError("rank/world of the process group do not match the communicator parameters")
+            if self.world != self.num_ranks_per_node:
+                raise RuntimeError("multi-node expert parallelism is not supported: one NVSwitch box only")
+
+    # reference API names
+    @staticmethod
+    def createUniqueId():
+        """The reference ships a TCP bootstrap id from rank 0; the rendezvous here belongs to torch.distributed."""
+        return torch.zeros(128, dtype=torch.uint8)
+
+    def getRank(self) -> int:
+        return self.rank
+
+    def getWorldSize(self) -> int:
+        return self.world
+
+    def getNumRanksPerNode(self) -> int:
+        return self.num_ranks_per_node
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    # ---- collectives used by the plans
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[n] -> [world, n] (every rank's copy of `t`)."""
+        if self.world == 1:
+            return t.reshape(1, -1)
+        out = torch.empty((self.world, t.numel()), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1), group=self.group)
+        return out
+
+    def exchange(self, sends: list[torch.Tensor | None], recvs: list[torch.Tensor | None]) -> None:
+        """Variable-size all-to-all: sends[p] goes to peer p, recvs[p] is filled by peer p.  Entries are
+        contiguous row slices (possibly empty or None); the slice for this rank itself is copied locally."""
+        me = self.rank
+        if sends[me] is not None and recvs[me] is not None and sends[me].numel():
+            if recvs[me].data_ptr() != sends[me].data_ptr():
+                recvs[me].copy_(sends[me])
+        if self.world == 1:
+            return
+        ops = []
+        for step in range(1, self.world):
+            dst = (me + step) % self.world
+            src = (me - step) % self.world
+            if sends[dst] is not None and sends[dst].numel():
+                ops.append(dist.P2POp(dist.isend, sends[dst], self._global(dst), group=self.group))
+            if recvs[src] is not None and recvs[src].numel():
+                ops.append(dist.P2POp(dist.irecv, recvs[src], self._global(src), group=self.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def _global(self, group_rank: int) -> int:
+        return group_rank if self.group is None else dist.get_global_rank(self.group, group_rank)
+
+
+# The reference's class name, so that code written against python/eps keeps importing.
+MscclppCommunicator = Communicator
+MscclppCommunicatorParams = CommunicatorParams

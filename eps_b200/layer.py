@@ -1,0 +1,127 @@
+"""The FP8 MoE expert layer on one rank of an expert-parallel group: the hot path end to end.
+
+  tokens bf16 --quant 1x128--> fp8 + scales --dispatch (unique token per rank)--> expert-contiguous rows
+  --grouped GEMM gate/up + SwiGLU + requant (tcgen05)--> fp8 activations
+  --grouped GEMM down x gate weight (tcgen05)--> bf16 rows --local reduce--> combine --global reduce
+  (+ identity experts, + shared expert)--> bf16 output
+
+It drives the same objects a caller of the reference would drive (Scheduler + a grouped-GEMM executor,
+reference python/eps/scheduler/scheduler.py and python/eps/executor/aok_grouped_gemm.py), staged the same way.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from ._lib import EpsError
+from .communication import Communicator
+from .scheduler import Scheduler
+
+
+class MoELayerFP8:
+    def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, max_tokens_per_gpu: int,
+                 w_gate_up, w_gate_up_scale, w_down, w_down_scale, comm: Communicator | None = None,
+                 shared=None, num_stages: int = 1, max_gemm_rows: int | None = None, device=None):
+        """w_gate_up [EL, 2I, H] e4m3 codes (gate rows first), w_gate_up_scale [EL, 2I/128, H/128] fp32,
+        w_down [EL, H, I], w_down_scale [EL, H/128, I/128]: this rank's experts.
+        shared: optional (w_gate_up [1, 2Is, H], scale, w_down [1, H, Is], scale) of an always-on expert."""
+        self.comm = comm if comm is not None else Communicator()
+        self.W = self.comm.getWorldSize()
+        self.H, self.I, self.E, self.k = hidden, inter, num_experts, top_k
+        self.EL = num_experts // self.W
+        self.S = num_stages
+        self.max_tok = max_tokens_per_gpu
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if hidden % 128 or inter % 128:
+            raise EpsError("hidden and intermediate sizes must be multiples of 128")
+        if tuple(w_gate_up.shape) != (self.EL, 2 * inter, hidden) or tuple(w_down.shape) != (self.EL, hidden, inter):
+            raise EpsError("expert weight shapes do not match (EL, 2I, H) / (EL, H, I)")
+        self.wgu, self.wgu_s, self.wd, self.wd_s = w_gate_up, w_gate_up_scale, w_down, w_down_scale
+        self.shared = shared
+        self.sched = Scheduler(top_k, num_experts, hidden, hidden // 128, max_tokens_per_gpu, self.comm, self.EL,
+                               input_dtype=torch.uint8, device=self.dev)
+        worst = max_tokens_per_gpu * self.W * min(top_k, self.EL)
+        self.max_gemm_rows = min(worst, max_gemm_rows if max_gemm_rows is not None else 2 * max_tokens_per_gpu * top_k)
+        D = max(self.max_gemm_rows, 1)
+        dev = self.dev
+        self.A = torch.empty((D, hidden), dtype=torch.uint8, device=dev)
+        self.A_s = torch.empty((D, hidden // 128), dtype=torch.float32, device=dev)
+        self.act = torch.empty((D, inter), dtype=torch.uint8, device=dev)
+        self.act_s = torch.empty((D, inter // 128), dtype=torch.float32, device=dev)
+        self.Y = torch.empty((D, hidden), dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        T = max(max_tokens_per_gpu, 1)
+        self.xq = torch.empty((T, hidden), dtype=torch.uint8, device=dev)
+        self.xs = torch.empty((T, hidden // 128), dtype=torch.float32, device=dev)
+        if shared is not None:
+            Is = shared[2].shape[2]
+            self.sh_act = torch.empty((T, Is), dtype=torch.uint8, device=dev)
+            self.sh_act_s = torch.empty((T, Is // 128), dtype=torch.float32, device=dev)
+            self.sh_out = torch.empty((T, hidden), dtype=torch.bfloat16, device=dev)
+            self._sh_excl = {}
+        self.kernel_launches = 0
+        self.gateup_events = None  # optional (start, end) torch.cuda.Event pair recorded around the gate/up GEMM
+
+    def forward(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor,
+                num_global_tokens: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x [T, H] bf16, expert_indices [T, k] int32 (negative = identity expert), expert_weights [T, k] fp32."""
+        T = x.shape[0]
+        if T > self.max_tok:
+            raise EpsError(f"{T} tokens exceed max_tokens_per_gpu {self.max_tok}")
+        sched, S, EL = self.sched, self.S, self.EL
+        n = 0
+        xq, xs = ops.per_token_group_quant_fp8(x, out=self.xq[:T], out_scales=self.xs[:T])
+        n += 1
+        Tg = num_global_tokens if num_global_tokens is not None else T * self.W
+        excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1)
+        n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
+        rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)
+        if rows_k > self.max_gemm_rows:
+            raise EpsError(f"{rows_k} possible GEMM rows exceed max_gemm_rows {self.max_gemm_rows}")
+        D = max(rows_k, 1)
+        sched.prologue(expert_weights, xq, xs, self.A_s[:D], raw_input=x)
+        n += 4  # gate weights, hidden rows, scales to send order; scales to GEMM order
+        row_w = sched.gemm_row_weights()
+        n += 1
+        eps_ = EL // S
+        for s in range(S):
+            sched.dispatch(s)
+            sched.gemm_expand(self.A[:D], s)
+            ex = excl[s * eps_:(s + 1) * eps_ + 1]
+            ev = self.gateup_events if s == 0 else None
+            if ev is not None:
+                ev[0].record()
+            ops.grouped_gemm_fp8(ops.GEMM_GATEUP, self.A[:D], self.A_s[:D], self.wgu[s * eps_:(s + 1) * eps_],
+                                 self.wgu_s[s * eps_:(s + 1) * eps_], ex, out=self.act[:D], out_scales=self.act_s[:D],
+                                 status=self.status)
+            if ev is not None:
+                ev[1].record()
+            ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.act[:D], self.act_s[:D], self.wd[s * eps_:(s + 1) * eps_],
+                                 self.wd_s[s * eps_:(s + 1) * eps_], ex, out=self.Y[:D], row_w=row_w,
+                                 status=self.status)
+            sched.local_reduce(self.Y[:D], s, pre_weighted=True)
+            sched.combine(s)
+            n += 4
+        shared_out = None
+        if self.shared is not None and T > 0:
+            sgu, sgu_s, sd, sd_s = self.shared
+            if T not in self._sh_excl:
+                self._sh_excl[T] = torch.tensor([0, T], dtype=torch.int32, device=self.dev)
+            sh_excl = self._sh_excl[T]
+            ops.grouped_gemm_fp8(ops.GEMM_GATEUP, xq, xs, sgu, sgu_s, sh_excl, out=self.sh_act[:T],
+                                 out_scales=self.sh_act_s[:T], status=self.status)
+            shared_out = ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.sh_act[:T], self.sh_act_s[:T], sd, sd_s,
+                                              sh_excl, out=self.sh_out[:T], status=self.status)
+            n += 2
+        if out is None:
+            out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device)
+        sched.epilogue(out, shared=shared_out, ref_arith=False)
+        n += 1
+        self.kernel_launches = n
+        return out
+
+    def check_status(self) -> None:
+        """Raises if a bounded device-side wait of a GEMM kernel expired (synchronises)."""
+        st = self.status.cpu().tolist()
+        if st[0] != 0:
+            raise EpsError(f"grouped GEMM gave up on a bounded wait (code {st[0]}, CTA {st[1]})")

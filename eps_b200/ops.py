@@ -77,12 +77,15 @@ def quant_block128(w):
 # ------------------------------------------------------------------ plans
 
 
-def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True):
+def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True, with_bounds=False):
+    """Source-side plans.  with_bounds=True also returns send_bounds = [0, send_incl...] (one buffer, so the
+    gathers can read their [begin, end) window from the device)."""
     _check(idx, "expert_indices", torch.int32, 2)
     T, k = idx.shape
     dev = idx.device
     send_map = torch.empty((max(T * W, 1),), dtype=torch.int32, device=dev)
-    send_incl = torch.empty((W * S,), dtype=torch.int32, device=dev)
+    send_bounds = torch.zeros((W * S + 1,), dtype=torch.int32, device=dev)
+    send_incl = send_bounds[1:]
     glob_map = torch.empty((max(T * W, 1),), dtype=torch.int32, device=dev) if want_global else None
     coll_incl = torch.empty((W * S,), dtype=torch.int32, device=dev) if want_global else None
     zero_scale = None
@@ -91,6 +94,8 @@ def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True):
         zero_scale = torch.empty((max(T, 1),), dtype=torch.float32, device=dev)
     call("epsb_source_plans", ptr(idx), ptr(weights), T, k, E, W, S, ptr(send_map), ptr(send_incl), ptr(glob_map),
          ptr(coll_incl), ptr(zero_scale), stream_ptr())
+    if with_bounds:
+        return send_map, send_incl, glob_map, coll_incl, zero_scale, send_bounds
     return send_map, send_incl, glob_map, coll_incl, zero_scale
 
 

@@ -511,6 +511,10 @@ void orc_grouped_gemm_fp8(const uint8_t* A, const float* a_s, const uint8_t* B, 
   for (int e = 0; e < E; e++) {
     const int m0 = excl[e], m1 = excl[e + 1];
     if (m1 <= m0) continue;
+    const int64_t rows = m1 - m0;
+    float* af = (float*)malloc(sizeof(float) * (size_t)rows * K); /* dequantised codes (scales applied later) */
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < rows * K; i++) af[i] = lut[A[(size_t)m0 * K + i]];
 #pragma omp parallel
     {
       float* wrow = (float*)malloc(sizeof(float) * (size_t)K);
@@ -519,22 +523,28 @@ void orc_grouped_gemm_fp8(const uint8_t* A, const float* a_s, const uint8_t* B, 
         const uint8_t* bp = B + ((size_t)e * N + n) * K;
         const float* bs = b_s + ((size_t)e * NB + n / 128) * KB;
         for (int64_t kk = 0; kk < K; kk++) wrow[kk] = lut[bp[kk]];
-        for (int m = m0; m < m1; m++) {
-          const uint8_t* ap = A + (size_t)m * K;
-          const float* as = a_s + (size_t)m * KB;
+        for (int64_t m = 0; m < rows; m++) {
+          const float* ap = af + (size_t)m * K;
+          const float* as = a_s + (size_t)(m0 + m) * KB;
           float acc = 0.0f;
           for (int64_t kb = 0; kb < KB; kb++) {
-            float part = 0.0f;
-            const uint8_t* a8 = ap + kb * 128;
+            /* 16 interleaved partial sums, reduced in a fixed order: vectorisable and deterministic */
+            float ps[16];
+            for (int j = 0; j < 16; j++) ps[j] = 0.0f;
+            const float* a8 = ap + kb * 128;
             const float* w8 = wrow + kb * 128;
-            for (int t = 0; t < 128; t++) part += lut[a8[t]] * w8[t];
+            for (int t = 0; t < 128; t += 16)
+              for (int j = 0; j < 16; j++) ps[j] += a8[t + j] * w8[t + j];
+            float part = 0.0f;
+            for (int j = 0; j < 16; j++) part += ps[j];
             acc += (as[kb] * bs[kb]) * part;
           }
-          C[(size_t)m * N + n] = acc;
+          C[(size_t)(m0 + m) * N + n] = acc;
         }
       }
       free(wrow);
     }
+    free(af);
   }
 }
 

@@ -259,7 +259,7 @@ def moe_layer_fp32(x_bits, idx, w, Wgu_q, Wgu_s, Wd_q, Wd_s, requant_act=True, s
     idx = _i32(idx)
     T, k = idx.shape
     E, two_i, H = Wgu_q.shape
-    xq, xs = quant_1x128(x_bits)
+    xq, xs = quant_1x128(x_bits, div_mode=1)
     order = []
     for e in range(E):
         tt, jj = np.nonzero(idx == e)

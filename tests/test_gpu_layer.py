@@ -1,0 +1,107 @@
+"""The whole FP8 MoE layer on one GPU against the fp32 dequantised oracle (tolerance: max |err| <= 2e-2 x
+output RMS, the standard the layer is specified to), and the Scheduler's reference-API flow."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _weights(cfg, experts, dev, oracle):
+    from eps_b200 import ops, workloads
+
+    gu, d = [], []
+    for e in experts:
+        a, b = workloads.make_expert_weights(cfg, e, inter=cfg.shared_inter if e < 0 else None)
+        gu.append(a)
+        d.append(b)
+    gu, d = torch.stack(gu), torch.stack(d)
+    gq, gs = ops.quant_block128(gu.to(dev))
+    dq, ds = ops.quant_block128(d.to(dev))
+    # weight codes and scales are bit-exact against the oracle
+    rq, rs = oracle.quant_block128(gu.float().numpy())
+    assert np.array_equal(gq.cpu().numpy(), rq) and np.array_equal(gs.cpu().numpy(), rs)
+    rdq, rds = oracle.quant_block128(d.float().numpy())
+    assert np.array_equal(dq.cpu().numpy(), rdq) and np.array_equal(ds.cpu().numpy(), rds)
+    return (gq, gs, dq, ds), (rq, rs, rdq, rds)
+
+
+LAYER_CASES = [
+    # T, H, I, E, k, n_zero, shared_I, stages
+    (64, 512, 256, 4, 2, 0, 0, 1),
+    (256, 2048, 1408 - 1408 % 128, 16, 4, 0, 0, 1),   # config 0 with I rounded to the 128 grid
+    (100, 1024, 512, 8, 4, 4, 256, 2),                # identity experts + shared expert, two stages
+    (33, 768, 384, 8, 8, 0, 0, 4),
+]
+
+
+@pytest.mark.parametrize("T,H,I,E,k,nz,sh,S", LAYER_CASES)
+def test_layer_vs_oracle(cuda, oracle, T, H, I, E, k, nz, sh, S):
+    from eps_b200 import workloads
+    from eps_b200.layer import MoELayerFP8
+
+    cfg = workloads.CONFIGS[0].scaled(tokens_per_rank=T, hidden=H, inter=I, num_experts=E, top_k=k,
+                                      num_zero_experts=nz, shared_inter=sh, bias="normal" if nz else "none")
+    x = workloads.make_tokens(cfg)
+    idx, w = workloads.make_routing(cfg)
+    dev_w, ref_w = _weights(cfg, range(E), cuda, oracle)
+    shared = ref_shared = None
+    if sh:
+        shared, ref_shared = _weights(cfg, [-1], cuda, oracle)
+    layer = MoELayerFP8(H, I, E, k, T, *dev_w, shared=shared, num_stages=S)
+    out = layer.forward(x.to(cuda), idx.to(cuda), w.to(cuda))
+    torch.cuda.synchronize()
+    layer.check_status()
+    want = oracle.moe_layer_fp32(_bits(x), idx.numpy(), w.numpy(), *ref_w, shared=ref_shared)
+    got = out.float().cpu().numpy()
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    err = float(np.max(np.abs(got - want)))
+    assert err <= 2e-2 * rms, f"max |err| {err:.3e} vs 2e-2 x RMS {2e-2 * rms:.3e}"
+    # a second call with other routing reuses the arenas
+    cfg2 = cfg.scaled(cfg_id=7)
+    idx2, w2 = workloads.make_routing(cfg2)
+    out2 = layer.forward(x.to(cuda), idx2.to(cuda), w2.to(cuda))
+    want2 = oracle.moe_layer_fp32(_bits(x), idx2.numpy(), w2.numpy(), *ref_w, shared=ref_shared)
+    assert float(np.max(np.abs(out2.float().cpu().numpy() - want2))) <= 2e-2 * float(np.sqrt(np.mean(want2 ** 2)))
+
+
+def test_scheduler_reference_flow_bf16(cuda, oracle):
+    """Drives Scheduler exactly like a caller of the reference (bf16 rows, reference arithmetic) with the
+    expert FFN replaced by the identity: output[t] = sum_j w[t,j] * x[t] over FFN slots + identity-expert term."""
+    from eps_b200.scheduler import Scheduler
+
+    T, H, E, k, S = 150, 2048, 16, 4, 2
+    rng = np.random.default_rng(0)
+    from helpers import random_routing
+
+    idx, w = random_routing(rng, T, k, E, 4)
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).to(cuda)
+    d_idx, d_w = torch.from_numpy(idx).to(cuda), torch.from_numpy(w).to(cuda)
+    sched = Scheduler(k, E, H, 0, T, None, E)
+    excl, n_recv = sched.rendezvous_and_plan(d_idx, d_w, T, S, False)
+    send_map, send_incl = oracle.comm_plan(idx, E, 1, S)
+    assert n_recv == send_incl[-1]
+    ridx = idx[send_map % T]
+    rexcl, _ = oracle.gemm_plan(ridx, k, 0, E, T, 1)
+    assert np.array_equal(excl.cpu().numpy(), rexcl)
+    sched.prologue(d_w, x)
+    D = int(rexcl[-1])
+    gemm_in = torch.zeros((D, H), dtype=torch.bfloat16, device=cuda)
+    for s in range(S):
+        sched.dispatch(s)
+        sched.gemm_expand(gemm_in, s)
+        sched.local_reduce(gemm_in, s)   # identity FFN
+        sched.combine(s)
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=cuda)
+    sched.epilogue(out)
+    torch.cuda.synchronize()
+    xf = x.float().cpu().numpy()
+    want = xf * w.sum(1, keepdims=True)  # FFN slots and identity slots both contribute w * x here
+    got = out.float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 3e-2 * np.abs(want).max()
+    with pytest.raises(Exception, match="Invalid num_stages"):
+        sched.rendezvous_and_plan(d_idx, d_w, T, 3, False)
