@@ -133,21 +133,30 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+// Asynchronous TMEM load of 32 columns of this warp's 32 lanes; the registers are valid only after
+// tmem_wait() on the same array (which ties them to the wait through read-write operands, so no use
+// can be scheduled above it).
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-#pragma unroll
-  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 struct GemmParams {
@@ -342,21 +351,34 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (!ok) break;
         tc_fence_after();
         const uint32_t tb = lane_addr + (uint32_t)buf * kBN;
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-          // gate/up mode: chunks 0,1 = gate columns [64*half, +64), chunks 2,3 = up columns [128+64*half, +64)
-          int col;
-          if (kMode == EPSB_GEMM_GATEUP) col = (ch < 2 ? 0 : 128) + 64 * half + (ch & 1) * 32;
-          else col = 128 * half + ch * 32;
-          float v[32];
-          tmem_ld32(tb + col, v);
+        // gate/up mode: chunks 0,1 = gate columns [64*half, +64), chunks 2,3 = up columns [128+64*half, +64)
+        auto col_of = [&](int ch) -> uint32_t {
+          if (kMode == EPSB_GEMM_GATEUP) return (uint32_t)((ch < 2 ? 0 : 128) + 64 * half + (ch & 1) * 32);
+          return (uint32_t)(128 * half + ch * 32);
+        };
+        auto fold = [&](int ch, const uint32_t (&r)[32]) {
           const float s = (kMode == EPSB_GEMM_GATEUP && ch >= 2) ? s1 : s0;
 #pragma unroll
-          for (int i = 0; i < 32; i++) acc[ch * 32 + i] = fmaf(v[i], s, acc[ch * 32 + i]);
-        }
+          for (int i = 0; i < 32; i++) acc[ch * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[ch * 32 + i]);
+        };
+        // Two register buffers: the load of chunk c+1 is in flight while chunk c is folded in.
+        uint32_t va[32], vb[32];
+        tmem_ld32_async(tb + col_of(0), va);
+        tmem_wait(va);
+        tmem_ld32_async(tb + col_of(1), vb);
+        fold(0, va);
+        tmem_wait(vb);
+        tmem_ld32_async(tb + col_of(2), va);
+        fold(1, vb);
+        tmem_wait(va);
+        tmem_ld32_async(tb + col_of(3), vb);
+        fold(2, va);
+        tmem_wait(vb);
+        // every TMEM read of this buffer has completed: hand it back before the last fold
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->tmem_empty[buf]);
+        fold(3, vb);
       }
       if (!ok) break;
 

@@ -47,6 +47,26 @@ gather_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, c
   }
 }
 
+// Rows that are not a multiple of 16 bytes (index / weight rows of k int32 or fp32): one 4-byte word per thread.
+__global__ void __launch_bounds__(kMoveThreads)
+gather_words_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, const int32_t* __restrict__ map,
+                    int32_t map_div, int32_t map_mod, const int32_t* __restrict__ bounds, int b0, int b1,
+                    int64_t n_rows, int words) {
+  int64_t begin = 0, end = n_rows;
+  if (bounds != nullptr) {
+    begin = bounds[b0];
+    end = bounds[b1];
+  }
+  const int64_t total = (end - begin) * words;
+  for (int64_t g = (int64_t)blockIdx.x * kMoveThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kMoveThreads) {
+    const int64_t i = begin + g / words;
+    const int c = (int)(g % words);
+    const int32_t m = __ldg(map + i);
+    const int64_t s = (int64_t)((m / map_div) % map_mod);
+    dst[i * words + c] = __ldg(src + s * words + c);
+  }
+}
+
 __global__ void __launch_bounds__(kMoveThreads)
 scatter_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, const int32_t* __restrict__ map,
                     int32_t div, int64_t n, int64_t row_bytes) {
@@ -118,10 +138,21 @@ using namespace epsb;
 extern "C" int epsb_gather_rows(const void* src, void* dst, const int32_t* map, int32_t map_div, int32_t map_mod,
                                 const int32_t* bounds, int b0, int b1, int64_t n_rows, int64_t max_rows,
                                 int64_t row_bytes, void* stream) {
-  int rc = check_rows(src, dst, row_bytes);
-  if (rc) return rc;
   EPSB_REQUIRE(map_div > 0 && map_mod > 0, EPSB_ERR_INVALID, "map_div/map_mod must be positive");
   const int64_t bound = bounds ? max_rows : n_rows;
+  if (row_bytes > 0 && row_bytes % 16 != 0) {
+    EPSB_REQUIRE(row_bytes % 4 == 0 && ((uintptr_t)src & 3) == 0 && ((uintptr_t)dst & 3) == 0, EPSB_ERR_INVALID,
+                 "row_bytes %lld is not a multiple of 4", (long long)row_bytes);
+    if (bound <= 0) return EPSB_OK;
+    const int words = (int)(row_bytes / 4);
+    int64_t blocks = (bound * words + kMoveThreads - 1) / kMoveThreads;
+    if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+    gather_words_kernel<<<(int)blocks, kMoveThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        (const uint32_t*)src, (uint32_t*)dst, map, map_div, map_mod, bounds, b0, b1, n_rows, words);
+    return check_launch("gather_rows(words)");
+  }
+  int rc = check_rows(src, dst, row_bytes);
+  if (rc) return rc;
   if (bound <= 0) return EPSB_OK;
   gather_rows_kernel<<<move_grid(bound), kMoveThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)src, (uint8_t*)dst, map, map_div, map_mod, bounds, b0, b1, n_rows, row_bytes);

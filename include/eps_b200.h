@@ -119,7 +119,9 @@ int epsb_fastep_plan(const int32_t* all_gathered, int my_rank, int W, int E, int
                      int32_t* arr_dst, void* stream);
 
 /* ----------------------------------------------------------------------------
- * Row movement.  row_bytes % 16 == 0, all row bases 16-byte aligned.
+ * Row movement.  row_bytes % 16 == 0 and all row bases 16-byte aligned, except
+ * epsb_gather_rows which also takes rows of any multiple of 4 bytes (the [k]
+ * index / weight rows).
  * -------------------------------------------------------------------------- */
 
 /* dst[i,:] = src[(map[i] / map_div) % map_mod, :] for i in [begin, end) where

@@ -14,7 +14,7 @@ def _dev(a, cuda):
     return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
 
 
-@pytest.mark.parametrize("rows,row_bytes", [(1, 16), (7, 32), (100, 7168), (64, 224), (33, 14336), (5, 4096 + 16)])
+@pytest.mark.parametrize("rows,row_bytes", [(1, 16), (7, 32), (100, 7168), (64, 224), (33, 14336), (5, 4096 + 16), (9, 8), (50, 12), (31, 48 + 4)])
 def test_gather_rows(cuda, rows, row_bytes):
     from eps_b200 import ops
 
