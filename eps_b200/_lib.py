@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libeps_b200.so")
+# EPS_B200_LIB selects another build of the same library (kernel A/B comparisons).
+LIB_PATH = os.environ.get("EPS_B200_LIB") or os.path.join(_HERE, "libeps_b200.so")
 
 _P = c_void_p
 _I = c_int
@@ -34,6 +35,7 @@ SIGNATURES = {
     "epsb_local_reduce": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _P, _P],
     "epsb_global_reduce_ref": [_P, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_global_reduce": [_P, _P, _P, _P, _P, _I, _I, _L, _P, _P],
+    "epsb_reduce_ep1": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_fastep_reduce": [_P, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_silu_run": [_P, _P, _P, _I, _L, _L, _P],
     "epsb_grouped_gemm_fp8": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _P, _P],

@@ -159,6 +159,19 @@ __device__ __forceinline__ void tmem_wait(uint32_t (&r)[32]) {
                : "memory");
 }
 
+// No instruction: makes later uses of r depend on this point of the (volatile) asm sequence, i.e. on the
+// tcgen05.wait::ld issued just before it.
+__device__ __forceinline__ void tmem_tie(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
 struct GemmParams {
   const float* a_s;
   const float* b_s;
@@ -250,6 +263,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const uint32_t tmem_base = sm->tmem_base;
   const int total_tiles = sm->tile_prefix[p.num_experts] * p.n_tiles;
 
+  // Register budget.  The CTA owns kThreads * 168 registers (what __launch_bounds__(384, 1) compiles to);
+  // setmaxnreg.inc BLOCKS until the CTA's own pool can serve it, so the two numbers below must satisfy
+  // 128 * dec + 256 * inc <= 384 * 168 = 64512, or the kernel hangs outside every bounded wait.
+  static_assert(128 * 40 + 256 * 232 <= kThreads * 168, "setmaxnreg budget exceeds the CTA's register pool");
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0 && lane == 0) {
@@ -337,48 +354,55 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
       for (int i = 0; i < 128; i++) acc[i] = 0.0f;
       float sa = __ldg(as_row), sb0 = __ldg(bs0), sb1 = __ldg(bs1);
+      float s0 = 0.0f, s1 = 0.0f;
+      // gate/up mode: chunks 0,1 = gate columns [64*half, +64), chunks 2,3 = up columns [128+64*half, +64)
+      auto col_of = [&](int ch) -> uint32_t {
+        if (kMode == EPSB_GEMM_GATEUP) return (uint32_t)((ch < 2 ? 0 : 128) + 64 * half + (ch & 1) * 32);
+        return (uint32_t)(128 * half + ch * 32);
+      };
+      auto tmem_of = [&](uint32_t k_it) -> uint32_t { return lane_addr + (k_it & 1u) * (uint32_t)kBN; };
+      auto wait_full = [&](uint32_t k_it) -> bool {
+        bool good = mbar_wait(&sm->tmem_full[k_it & 1u], (k_it >> 1) & 1u, sm, p.status, 31);
+        good = __all_sync(0xffffffffu, good);
+        if (good) tc_fence_after();
+        return good;
+      };
+      // Drain of one K step: two tcgen05.ld of 32 columns are issued together and awaited once (two
+      // waits per K step, 64 temporaries beside the 128 accumulators: no spills at 232 registers).  Measured
+      // on B200 the K-step period is set by the MMA <-> epilogue hand-off latency over the two TMEM buffers
+      // (~0.7 us), not by these loads, the scale loads or the fold; deeper register pipelines only spilled.
+      uint32_t t0[32], t1[32];
       for (int kb = 0; kb < KB; kb++, it++) {
-        const int buf = it & 1;
-        const uint32_t tph = (it >> 1) & 1;
-        const float s0 = sa * sb0, s1 = sa * sb1;
+        s0 = sa * sb0;
+        s1 = sa * sb1;
         if (kb + 1 < KB) {
           sa = __ldg(as_row + kb + 1);
           sb0 = __ldg(bs0 + kb + 1);
           sb1 = __ldg(bs1 + kb + 1);
         }
-        ok = mbar_wait(&sm->tmem_full[buf], tph, sm, p.status, 31);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = wait_full(it);
         if (!ok) break;
-        tc_fence_after();
-        const uint32_t tb = lane_addr + (uint32_t)buf * kBN;
-        // gate/up mode: chunks 0,1 = gate columns [64*half, +64), chunks 2,3 = up columns [128+64*half, +64)
-        auto col_of = [&](int ch) -> uint32_t {
-          if (kMode == EPSB_GEMM_GATEUP) return (uint32_t)((ch < 2 ? 0 : 128) + 64 * half + (ch & 1) * 32);
-          return (uint32_t)(128 * half + ch * 32);
-        };
-        auto fold = [&](int ch, const uint32_t (&r)[32]) {
-          const float s = (kMode == EPSB_GEMM_GATEUP && ch >= 2) ? s1 : s0;
+        const uint32_t tb = tmem_of(it);
+        tmem_ld32_async(tb + col_of(0), t0);
+        tmem_ld32_async(tb + col_of(1), t1);
+        tmem_wait(t0);
+        tmem_tie(t1);
 #pragma unroll
-          for (int i = 0; i < 32; i++) acc[ch * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[ch * 32 + i]);
-        };
-        // Two register buffers: the load of chunk c+1 is in flight while chunk c is folded in.
-        uint32_t va[32], vb[32];
-        tmem_ld32_async(tb + col_of(0), va);
-        tmem_wait(va);
-        tmem_ld32_async(tb + col_of(1), vb);
-        fold(0, va);
-        tmem_wait(vb);
-        tmem_ld32_async(tb + col_of(2), va);
-        fold(1, vb);
-        tmem_wait(va);
-        tmem_ld32_async(tb + col_of(3), vb);
-        fold(2, va);
-        tmem_wait(vb);
-        // every TMEM read of this buffer has completed: hand it back before the last fold
+        for (int i = 0; i < 32; i++) acc[i] = fmaf(__uint_as_float(t0[i]), s0, acc[i]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[32 + i] = fmaf(__uint_as_float(t1[i]), s0, acc[32 + i]);
+        tmem_ld32_async(tb + col_of(2), t0);
+        tmem_ld32_async(tb + col_of(3), t1);
+        tmem_wait(t0);
+        tmem_tie(t1);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm->tmem_empty[buf]);
-        fold(3, vb);
+        if (lane == 0) mbar_arrive(&sm->tmem_empty[it & 1u]);
+        const float sc = kMode == EPSB_GEMM_GATEUP ? s1 : s0;
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[64 + i] = fmaf(__uint_as_float(t0[i]), sc, acc[64 + i]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[96 + i] = fmaf(__uint_as_float(t1[i]), sc, acc[96 + i]);
       }
       if (!ok) break;
 

@@ -33,7 +33,19 @@ __device__ __forceinline__ SortScratch carve(int32_t* smem, int B) {
   return s;
 }
 
-size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)(kPlanWarps + 2) * B + kPlanWarps + 1); }
+size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)(kPlanWarps + 2) * B + kPlanWarps + 2); }
+
+// Shared memory left for the key cache (uint16 per item) after the scratch of a B-bucket sort.
+constexpr size_t kPlanSmemBudget = 200 * 1024;
+size_t key_cache_bytes(int B, int64_t n_items) {
+  const size_t need = ((size_t)n_items * 2 + 15) & ~(size_t)15;
+  const size_t used = sort_smem_bytes(B);
+  return used + need <= kPlanSmemBudget ? need : 0;
+}
+__device__ __forceinline__ uint16_t* cache_after(int32_t* smem, int B, int cache_items) {
+  if (cache_items <= 0) return nullptr;
+  return reinterpret_cast<uint16_t*>(smem + (kPlanWarps + 2) * B + kPlanWarps + 2);
+}
 
 // Inclusive scan of one value per thread over the whole 1024-thread CTA.
 __device__ __forceinline__ int block_inclusive_scan(int v, int32_t* wsum) {
@@ -84,11 +96,14 @@ __device__ __forceinline__ int strided_order(int v, int n, int NT) {
 // Positions 0..n_pos-1 are already in visiting order.  On return s.base/s.total
 // hold the exclusive bucket offsets and the bucket sizes.
 template <class P>
-__device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
+__device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16_t* key_cache = nullptr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned lt_mask = (1u << lane) - 1u;
   // Items (position, slot) are numbered position-major; a warp owns a contiguous range of items and
-  // visits it 32 at a time, so the lane order inside a step is the visiting order.
+  // visits it 32 at a time, so the lane order inside a step is the visiting order.  Keys of kKeyUnroll
+  // steps are fetched together (independent global loads in flight) and, when the caller provides room,
+  // cached in shared memory so that the emission pass does not touch global memory for them again.
+  constexpr int kKeyUnroll = 4;
   const int J = p.slots();
   const int n_items = n_pos * J;
   const int chunk = ((n_items + kPlanThreads - 1) / kPlanThreads) * 32;
@@ -96,13 +111,24 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
   for (int i = threadIdx.x; i < kPlanWarps * B; i += kPlanThreads) s.rows[i] = 0;
   __syncthreads();
   int32_t* my_row = s.rows + warp * B;
-  for (int i0 = i_begin; i0 < i_end; i0 += 32) {
-    const int i = i0 + lane;
-    const bool live = i < i_end;
-    const int key = live ? p.key(i / J, i % J) : -1;
-    const unsigned m = __match_any_sync(0xffffffffu, key);
-    if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
-    __syncwarp();
+  for (int i0 = i_begin; i0 < i_end; i0 += 32 * kKeyUnroll) {
+    int keys[kKeyUnroll];
+#pragma unroll
+    for (int u = 0; u < kKeyUnroll; u++) {
+      const int i = i0 + u * 32 + lane;
+      keys[u] = i < i_end ? p.key(i / J, i % J) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < kKeyUnroll; u++) {
+      const int i = i0 + u * 32 + lane;
+      if (i0 + u * 32 < i_end) {  // warp-uniform
+        const int key = keys[u];
+        if (key_cache != nullptr && i < i_end) key_cache[i] = (uint16_t)key;  // -1 -> 0xffff
+        const unsigned m = __match_any_sync(0xffffffffu, key);
+        if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+        __syncwarp();
+      }
+    }
   }
   __syncthreads();
   for (int b = threadIdx.x; b < B; b += kPlanThreads) {
@@ -122,20 +148,31 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s) {
     if (threadIdx.x < B) s.base[threadIdx.x] = inc - v;
   }
   __syncthreads();
-  for (int i0 = i_begin; i0 < i_end; i0 += 32) {
-    const int i = i0 + lane;
-    const bool live = i < i_end;
-    const int pos = i / J, j = i % J;
-    const int key = live ? p.key(pos, j) : -1;
-    const unsigned m = __match_any_sync(0xffffffffu, key);
-    int mine = 0;
-    if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
-    __syncwarp();
-    if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
-    __syncwarp();
-    if (live) {
-      if (key >= 0) p.emit(pos, j, mine);
-      else p.skip(pos, j);
+  for (int i0 = i_begin; i0 < i_end; i0 += 32 * kKeyUnroll) {
+    int keys[kKeyUnroll];
+#pragma unroll
+    for (int u = 0; u < kKeyUnroll; u++) {
+      const int i = i0 + u * 32 + lane;
+      if (i >= i_end) keys[u] = -1;
+      else if (key_cache != nullptr) keys[u] = key_cache[i] == 0xffffu ? -1 : (int)key_cache[i];
+      else keys[u] = p.key(i / J, i % J);
+    }
+#pragma unroll
+    for (int u = 0; u < kKeyUnroll; u++) {
+      const int i = i0 + u * 32 + lane;
+      if (i0 + u * 32 < i_end) {  // warp-uniform
+        const int key = keys[u];
+        const unsigned m = __match_any_sync(0xffffffffu, key);
+        int mine = 0;
+        if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
+        __syncwarp();
+        if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
+        __syncwarp();
+        if (i < i_end) {
+          if (key >= 0) p.emit(i / J, i % J, mine);
+          else p.skip(i / J, i % J);
+        }
+      }
     }
   }
   __syncthreads();
@@ -199,10 +236,11 @@ struct GlobalPlanProblem {
 __global__ void __launch_bounds__(kPlanThreads, 1)
 source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weights, int T, int k, int E, int W,
                     int S, int32_t* send_map, int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl,
-                    float* zero_scale) {
+                    float* zero_scale, int cache_items) {
   extern __shared__ int32_t plan_smem[];
   const int EL = E / W;
   SortScratch s = carve(plan_smem, E);
+  uint16_t* cache = cache_after(plan_smem, E, cache_items);
   if (zero_scale != nullptr && weights != nullptr) {
     for (int t = threadIdx.x; t < T; t += kPlanThreads) {
       float z = 0.0f;
@@ -214,14 +252,14 @@ source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w
   int NT = (T + 15) / 16;
   NT = max(1, min(NT, 128));
   CommPlanProblem cp{idx, send_map, T, k, W, EL, NT};
-  stable_bucket_sort(cp, T, E, s);
+  stable_bucket_sort(cp, T, E, s, cache);
   write_stage_sums(s, W, EL, S, send_incl);
   if (glob_map == nullptr) return;
   const int n_sent = s.base[E - 1] + s.total[E - 1];
   for (int i = threadIdx.x; i < T * W; i += kPlanThreads) glob_map[i] = T * W;
   __syncthreads();  // send_map and the glob_map fill are visible to the whole CTA
   GlobalPlanProblem gp{idx, send_map, glob_map, T, k, W, EL};
-  stable_bucket_sort(gp, n_sent, E, s);
+  stable_bucket_sort(gp, n_sent, E, s, cache);
   write_stage_sums(s, W, EL, S, coll_incl);
 }
 
@@ -300,14 +338,16 @@ struct LocalReducePlanProblem {
 __global__ void __launch_bounds__(kPlanThreads, 1)
 expert_plans_kernel(const int32_t* __restrict__ ridx, const int32_t* __restrict__ recv_incl, int k, int lo, int hi,
                     int W, int S, int NT, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm, int32_t* scale_map,
-                    int32_t* red_map, int32_t* ret_incl) {
+                    int32_t* red_map, int32_t* ret_incl, int cache_items) {
   extern __shared__ int32_t plan_smem[];
   const int EL = hi - lo;
   const int R = recv_incl[W * S - 1];
+  // the cache sits behind the larger of the two scratch layouts so that both sorts can use it
+  uint16_t* cache = cache_after(plan_smem, scale_map != nullptr ? W * EL : EL, cache_items);
   {
     SortScratch s = carve(plan_smem, EL);
     GemmPlanProblem gp{ridx, gemm_map, inv_gemm, R, k, lo, hi, NT};
-    stable_bucket_sort(gp, R, EL, s);
+    stable_bucket_sort(gp, R, EL, s, cache);
     for (int e = threadIdx.x; e < EL; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
     if (threadIdx.x == 0) excl[0] = 0;
   }
@@ -315,7 +355,7 @@ expert_plans_kernel(const int32_t* __restrict__ ridx, const int32_t* __restrict_
   __syncthreads();  // inv_gemm is complete and visible
   SortScratch s = carve(plan_smem, W * EL);
   LocalReducePlanProblem lp{ridx, recv_incl, inv_gemm, scale_map, red_map, k, lo, hi, W, S, EL};
-  stable_bucket_sort(lp, R, W * EL, s);
+  stable_bucket_sort(lp, R, W * EL, s, cache);
   write_stage_sums(s, W, EL, S, ret_incl);
 }
 
@@ -425,11 +465,12 @@ extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T
     if (coll_incl) cudaMemsetAsync(coll_incl, 0, sizeof(int32_t) * W * S, st);
     return check_launch("source_plans(T=0)");
   }
-  const size_t smem = sort_smem_bytes(E);
+  const size_t cache = key_cache_bytes(E, (int64_t)T * W);
+  const size_t smem = sort_smem_bytes(E) + cache;
   int rc = set_smem((const void*)source_plans_kernel, smem);
   if (rc) return rc;
   source_plans_kernel<<<1, kPlanThreads, smem, st>>>(idx, weights, T, k, E, W, S, send_map, send_incl, glob_map,
-                                                     coll_incl, zero_scale);
+                                                     coll_incl, zero_scale, cache ? (int)((int64_t)T * W) : 0);
   return check_launch("source_plans");
 }
 
@@ -458,11 +499,14 @@ extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, 
   int NT = (int)((tot + 15) / 16);
   if (NT > 128) NT = 128;
   if (NT < 1) NT = 1;
-  const size_t smem = sort_smem_bytes(scale_map ? W * EL : EL);
+  const int Bmax = scale_map ? W * EL : EL;
+  const size_t cache = key_cache_bytes(Bmax, max_rows * k);
+  const size_t smem = sort_smem_bytes(Bmax) + cache;
   int rc = set_smem((const void*)expert_plans_kernel, smem);
   if (rc) return rc;
   expert_plans_kernel<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      ridx, recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl);
+      ridx, recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl,
+      cache ? (int)(max_rows * k) : 0);
   return check_launch("expert_plans");
 }
 

@@ -133,6 +133,54 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
   }
 }
 
+// ---------------------------------------------------------------- world of one: local + global reduce in one pass
+
+// out[t,:] = bf16( sum_j float(y[red_map[q,j],:]) + shared[t,:] + x[t,:] * zero_scale[t] ), q = glob_map[t]
+// (the return row of token t; with one rank the return buffer IS the collect buffer).  fp32 accumulation in
+// slot order, one rounding.  Replaces local_reduce -> (no-op exchange) -> global_reduce for ep_world_size 1.
+__global__ void __launch_bounds__(kRedThreads)
+reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red_map,
+                  const int32_t* __restrict__ glob_map, const int32_t* __restrict__ ret_incl, int S,
+                  const uint8_t* __restrict__ shared, const uint8_t* __restrict__ x,
+                  const float* __restrict__ zero_scale, int T, int k, int64_t H, uint8_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kRedWarps + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * kRedWarps;
+  const int vecs = (int)(H >> 3);
+  const int64_t row_bytes = H * 2;
+  const int64_t sentinel = (int64_t)ret_incl[S - 1] * k;
+  for (int64_t t = warp; t < T; t += n_warps) {
+    const int32_t q = __ldg(glob_map + t);
+    int32_t rows[kMaxSlots];
+#pragma unroll
+    for (int j = 0; j < kMaxSlots; j++) {
+      rows[j] = -1;
+      if (j < k && q < T) {
+        const int32_t r = __ldg(red_map + (int64_t)q * k + j);
+        if (r < sentinel) rows[j] = r;
+      }
+    }
+    const float zs = zero_scale != nullptr ? __ldg(zero_scale + t) : 0.0f;
+    for (int v = lane; v < vecs; v += 32) {
+      const int64_t off = t * row_bytes + (int64_t)v * 16;
+      uint4 in[kMaxSlots];
+#pragma unroll
+      for (int j = 0; j < kMaxSlots; j++)
+        if (j < k && rows[j] >= 0) in[j] = ld_nc_16(y + (int64_t)rows[j] * row_bytes + (int64_t)v * 16);
+      uint4 sh = make_uint4(0, 0, 0, 0), xin = make_uint4(0, 0, 0, 0);
+      if (shared != nullptr) sh = ld_nc_16(shared + off);
+      if (zero_scale != nullptr) xin = ld_nc_16(x + off);
+      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int j = 0; j < kMaxSlots; j++)
+        if (j < k && rows[j] >= 0) acc_f32(a, in[j]);
+      if (shared != nullptr) acc_f32(a, sh);
+      if (zero_scale != nullptr) fma_f32(a, xin, zs);
+      st_16(out + off, pack8(a));
+    }
+  }
+}
+
 // ---------------------------------------------------------------- global reduce (source rank)
 
 template <bool kRefArith>
@@ -417,6 +465,21 @@ extern "C" int epsb_global_reduce_ref(const void* recv, const int32_t* glob_map,
 extern "C" int epsb_global_reduce(const void* recv, const int32_t* glob_map, const void* shared, const void* x,
                                   const float* zero_scale, int T, int W, int64_t H, void* out, void* stream) {
   return launch_global_reduce<false>(recv, glob_map, shared, x, zero_scale, T, W, H, out, stream);
+}
+
+extern "C" int epsb_reduce_ep1(const void* y, const int32_t* red_map, const int32_t* glob_map, const int32_t* ret_incl,
+                               int S, const void* shared, const void* x, const float* zero_scale, int T, int k,
+                               int64_t H, void* out, void* stream) {
+  int rc = check_h(H);
+  if (rc) return rc;
+  EPSB_REQUIRE(k > 0 && k <= kMaxSlots, EPSB_ERR_INVALID, "topk %d exceeds %d", k, kMaxSlots);
+  EPSB_REQUIRE(S > 0, EPSB_ERR_INVALID, "num_stages %d", S);
+  EPSB_REQUIRE(zero_scale == nullptr || x != nullptr, EPSB_ERR_INVALID, "zero_scale needs the raw input x");
+  if (T <= 0) return EPSB_OK;
+  reduce_ep1_kernel<<<red_grid(T), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)y, red_map, glob_map, ret_incl, S, (const uint8_t*)shared, (const uint8_t*)x, zero_scale, T, k, H,
+      (uint8_t*)out);
+  return check_launch("reduce_ep1");
 }
 
 extern "C" int epsb_fastep_reduce(const void* rows, const void* raw, const void* shared, const float* w,

@@ -99,9 +99,11 @@ class MoELayerFP8:
             ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.act[:D], self.act_s[:D], self.wd[s * eps_:(s + 1) * eps_],
                                  self.wd_s[s * eps_:(s + 1) * eps_], ex, out=self.Y[:D], row_w=row_w,
                                  status=self.status)
-            sched.local_reduce(self.Y[:D], s, pre_weighted=True)
-            sched.combine(s)
-            n += 4
+            if self.W > 1:
+                sched.local_reduce(self.Y[:D], s, pre_weighted=True)
+                sched.combine(s)
+                n += 1
+            n += 3
         shared_out = None
         if self.shared is not None and T > 0:
             sgu, sgu_s, sd, sd_s = self.shared
@@ -115,7 +117,10 @@ class MoELayerFP8:
             n += 2
         if out is None:
             out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device)
-        sched.epilogue(out, shared=shared_out, ref_arith=False)
+        if self.W > 1:
+            sched.epilogue(out, shared=shared_out, ref_arith=False)
+        else:
+            sched.reduce_single_rank(self.Y[:D], out, shared=shared_out)
         n += 1
         self.kernel_launches = n
         return out

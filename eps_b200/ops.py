@@ -223,6 +223,16 @@ def global_reduce(recv, glob_map, out, W, shared=None, x=None, zero_scale=None, 
     return out
 
 
+def reduce_ep1(y, red_map, glob_map, ret_incl, S, k, out, shared=None, x=None, zero_scale=None):
+    """ep_world_size == 1: out[t] = sum_j y[red_map[glob_map[t], j]] (+shared) (+x*zero_scale), fp32, one rounding."""
+    _check(y, "gemm_output", torch.bfloat16, 2)
+    _check(out, "output", torch.bfloat16, 2)
+    T, H = out.shape
+    call("epsb_reduce_ep1", ptr(y), ptr(red_map), ptr(glob_map), ptr(ret_incl), S, ptr(shared), ptr(x),
+         ptr(zero_scale), T, k, H, ptr(out), stream_ptr())
+    return out
+
+
 def fastep_reduce(rows, raw, w, mapping, out, shared=None):
     _check(out, "out_tokens", torch.bfloat16, 2)
     _check(w, "weights", torch.float32, 2)

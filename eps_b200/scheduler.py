@@ -224,6 +224,16 @@ class Scheduler:
         ops.global_reduce(self.recv_out, ctx.glob_map, output, self.W, shared=shared, x=x if zero is not None else None,
                           zero_scale=zero, ref_arith=ref_arith)
 
+    def reduce_single_rank(self, gemm_output: torch.Tensor, output: torch.Tensor, shared=None) -> None:
+        """ep_world_size == 1 only: local_reduce(all stages) + combine + epilogue in one kernel, rows pre-weighted."""
+        if self.W != 1:
+            raise EpsError("reduce_single_rank needs ep_world_size == 1")
+        ctx = self.context
+        x = ctx.raw_input
+        zero = ctx.zero_scale if (x is not None and x.dtype == torch.bfloat16) else None
+        ops.reduce_ep1(gemm_output, ctx.red_map, ctx.glob_map, ctx.ret_incl, ctx.num_stages, self.top_k, output,
+                       shared=shared, x=x if zero is not None else None, zero_scale=zero)
+
     # helper used by the fused layer
     def gemm_row_weights(self) -> torch.Tensor:
         ctx = self.context

@@ -30,7 +30,7 @@ extern "C" {
 #define EPSB_OK 0
 #define EPSB_ERR_INVALID 1  /* bad argument / unsupported shape (reference: std::runtime_error) */
 #define EPSB_ERR_CUDA 2     /* a CUDA runtime/driver call failed */
-#define EPSB_ERR_TIMEOUT 3  /* a bounded device-side wait gave up (see epsb_gemm_status) */
+#define EPSB_ERR_TIMEOUT 3  /* a bounded device-side wait gave up (word 0 of the GEMM's status buffer) */
 #define EPSB_ERR_WORKSPACE 4 /* workspace too small */
 
 const char* epsb_last_error(void);
@@ -42,9 +42,9 @@ int epsb_version(void);
  *
  * x: [rows, cols] bf16 row-major, cols % 128 == 0.
  * q: [rows, cols] e4m3 codes.  scales: [rows, cols/128] fp32 row-major.
- * div_mode 0: scale = amax/448 with IEEE division (the layer contract).
- * div_mode 1: scale = div.full.f32(amax, 448), the instruction the reference
- *             kernel uses (fp8.cu:272-275), for bit-parity with that kernel.
+ * div_mode 1: scale = div.full.f32(amax, 448), the instruction the reference kernel uses (fp8.cu:272-275);
+ *             bit-identical to that kernel (on B200 it equals amax * fl(1/448) for every input).
+ * div_mode 0: scale = amax/448 with IEEE division (differs from mode 1 by 1 ulp on ~59 % of scales).
  * -------------------------------------------------------------------------- */
 int epsb_quant_1x128(const void* x, int64_t rows, int64_t cols, void* q, float* scales, int div_mode, void* stream);
 
@@ -174,6 +174,15 @@ int epsb_global_reduce_ref(const void* recv, const int32_t* glob_map, const void
 int epsb_global_reduce(const void* recv, const int32_t* glob_map, const void* shared, const void* x,
                        const float* zero_scale, int T, int W, int64_t H, void* out, void* stream);
 
+/* World of one (ep_world_size == 1): local reduce, the (empty) exchange and the global reduce in one pass.
+ * out[t,:] = bf16(sum_j float(y[red_map[q,j],:]) (+shared[t,:]) (+x[t,:]*zero_scale[t])), q = glob_map[t],
+ * y rows pre-weighted, fp32 accumulation in slot order, one rounding.
+ * ref: the chain localReduce -> All2All -> globalReduce -> zeroReduce (src/scheduler/scheduler.cu:171-228)
+ * when every peer is the rank itself. */
+int epsb_reduce_ep1(const void* y, const int32_t* red_map, const int32_t* glob_map, const int32_t* ret_incl, int S,
+                    const void* shared, const void* x, const float* zero_scale, int T, int k, int64_t H, void* out,
+                    void* stream);
+
 /* fast_ep combine: out[t,:] = bf16(sum_j w[t,j]*row(mapping[t*k+j]) (+shared)),
  * fp32 FMA accumulation; mapping >= 1000000 reads raw token mapping-1000000.
  * ref: fast_ep reduce (fast_ep_kernels.cu:231-335). */
@@ -206,7 +215,7 @@ int epsb_silu_run(const void* gate_up, void* act, const int32_t* exclusive_sum, 
  *
  * status: optional int32[4] device words; word 0 is set nonzero if a bounded
  * device-side wait expired (the kernel then drains and exits instead of
- * hanging).  Read it with epsb_gemm_status after synchronising.
+ * hanging); word 1 holds the CTA that gave up.  Read it after synchronising.
  *
  * mode EPSB_GEMM_PLAIN : C [max_rows, N] bf16 = result.
  * mode EPSB_GEMM_GATEUP: N = 2I, B rows are [gate(I) | up(I)] (activations.cu:19-20);

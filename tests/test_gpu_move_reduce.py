@@ -229,3 +229,45 @@ def test_silu(cuda, rows, I):
     assert torch.all(got[0] == 0) and torch.all(got[-1] == 0)
     # __expf is within a few ulp of expf; one bf16 ulp of slack
     assert bool(((got[1:-1] - want[1:-1]).abs() <= want[1:-1].abs() * 2.0 ** -7 + 1e-30).all())
+
+
+@pytest.mark.parametrize("T,k,H,S,shared,zero", [(40, 4, 512, 2, True, True), (300, 8, 7168, 1, False, False), (9, 12, 256, 3, True, False)])
+def test_reduce_ep1_matches_two_pass_semantics(cuda, oracle, T, k, H, S, shared, zero):
+    """World of one: the fused pass equals sum over the token's GEMM rows (+shared, +x*zero_scale) in fp32."""
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(T + k)
+    R = T - 2                         # two tokens have only identity experts: no return row
+    D = R * 2
+    red_map = np.full((R, k), R * k, dtype=np.int32)
+    perm = rng.permutation(D)
+    p = 0
+    for q in range(R):
+        for j in rng.choice(k, rng.integers(1, min(k, 2) + 1), replace=False):
+            red_map[q, j] = perm[p]
+            p += 1
+    ret_incl = np.sort(np.concatenate([rng.integers(0, R + 1, S - 1), [R]])).astype(np.int32)
+    glob = np.full(T, T, dtype=np.int32)
+    toks = rng.permutation(T)[:R]
+    glob[toks] = np.arange(R)
+    y = torch.randn((D, H), generator=torch.Generator().manual_seed(T)).to(torch.bfloat16)
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(T + 1)).to(torch.bfloat16)
+    sh = torch.randn((T, H), generator=torch.Generator().manual_seed(T + 2)).to(torch.bfloat16) if shared else None
+    zs = torch.rand((T,), generator=torch.Generator().manual_seed(T + 3)) if zero else None
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=cuda)
+    ops.reduce_ep1(y.to(cuda), _dev(red_map, cuda), _dev(glob, cuda), _dev(ret_incl, cuda), S, k, out,
+                   shared=None if sh is None else sh.to(cuda), x=x.to(cuda), zero_scale=None if zs is None else zs.to(cuda))
+    yf = y.float().numpy()
+    want = np.zeros((T, H), dtype=np.float32)
+    for t in range(T):
+        acc = np.zeros(H, dtype=np.float32)
+        if glob[t] < T:
+            for j in range(k):
+                if red_map[glob[t], j] < R * k:
+                    acc = acc + yf[red_map[glob[t], j]]
+        if shared:
+            acc = acc + sh[t].float().numpy()
+        if zero:
+            acc = (x[t].float().numpy().astype(np.float64) * np.float64(zs[t].item()) + acc.astype(np.float64)).astype(np.float32)
+        want[t] = acc
+    assert np.array_equal(_bits(out), oracle.bf16_bits(want))
