@@ -97,7 +97,10 @@ def test_quant_full_size_properties(cuda):
     q, s = ops.per_token_group_quant_fp8(x, div_mode=0)
     d = ops.per_token_group_dequant_fp8(q, s)
     amax = x.float().view(4096, 56, 128).abs().amax(-1)
-    assert torch.equal(s, amax / 448.0)
+    # torch divides a CUDA tensor by a scalar as a multiplication by its reciprocal, so take the quotient in fp64
+    assert torch.equal(s, (amax.double() / 448.0).float())
+    _, s1 = ops.per_token_group_quant_fp8(x, div_mode=1)
+    assert torch.equal(s1, amax * torch.tensor(1.0 / 448.0, dtype=torch.float32, device=cuda))
     err = (d.float() - x.float()).view(4096, 56, 128).abs().amax(-1)
     assert bool((err <= amax * 2.0 ** -4 + amax * 2.0 ** -8).all())
     q2, s2 = ops.per_token_group_quant_fp8(d, div_mode=0)
