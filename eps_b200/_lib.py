@@ -26,6 +26,7 @@ SIGNATURES = {
     "epsb_source_plans": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P],
     "epsb_recv_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
     "epsb_expert_plans": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P],
+    "epsb_expert_plans_noalloc": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P],
     "epsb_fastep_expand_plan": [_P, _I, _I, _I, _P, _P, _P],
     "epsb_fastep_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "epsb_gather_rows": [_P, _P, _P, c_int32, c_int32, _P, _I, _I, _L, _L, _L, _P],

@@ -7,6 +7,8 @@
 // per warp, counted per warp with warp-match votes (no atomics), scanned over
 // warps and over buckets, and emitted by rank.  The outputs are bit-identical
 // to the reference's, including for inputs that repeat an expert id inside a token.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace epsb {
@@ -436,6 +438,34 @@ fastep_plan_kernel(const int32_t* __restrict__ ag, int my_rank, int W, int E, in
   }
 }
 
+// ---------------------------------------------------------------- scratch that nobody has to allocate
+
+// Backing store of epsb_expert_plans_noalloc: the inverse GEMM map (one int32 per received (row, slot)).
+// It lives in the library's device image, so every GPU that loads the library holds these 4 MiB until exit.
+constexpr int64_t kStaticScratchItems = 1 << 20;
+static __device__ __align__(256) int32_t g_inv_gemm_scratch[kStaticScratchItems];
+
+// Device address of the array on the CURRENT device.  In host code the array's name is only a handle: the
+// address a kernel may use comes from cudaGetSymbolAddress, asked once per device with that device current.
+int static_inv_gemm_scratch(int32_t** out) {
+  static std::mutex mu;
+  static int32_t* per_device[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(EPSB_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(EPSB_ERR_INVALID, "device ordinal %d is outside the table of 64", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    int32_t* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_inv_gemm_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(EPSB_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    per_device[dev] = p;
+  }
+  *out = per_device[dev];
+  return EPSB_OK;
+}
+
 int set_smem(const void* fn, size_t bytes) {
   if (bytes > 227 * 1024) return fail(EPSB_ERR_INVALID, "plan needs %zu bytes of shared memory (> 227 KB)", bytes);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -508,6 +538,22 @@ extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, 
       ridx, recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl,
       cache ? (int)(max_rows * k) : 0);
   return check_launch("expert_plans");
+}
+
+extern "C" int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W,
+                                         int S, int max_tok_per_gpu, int64_t max_rows, int32_t* excl,
+                                         int32_t* gemm_map, int32_t* scale_map, int32_t* red_map, int32_t* ret_incl,
+                                         void* stream) {
+  EPSB_REQUIRE(k > 0 && max_rows >= 0, EPSB_ERR_INVALID, "bad sizes k=%d max_rows=%lld", k, (long long)max_rows);
+  EPSB_REQUIRE(max_rows * k <= kStaticScratchItems, EPSB_ERR_WORKSPACE,
+               "max_rows * topk = %lld exceeds the built-in scratch of %lld entries; use epsb_expert_plans with a "
+               "caller-provided inv_gemm buffer",
+               (long long)(max_rows * k), (long long)kStaticScratchItems);
+  int32_t* scratch = nullptr;
+  int rc = static_inv_gemm_scratch(&scratch);
+  if (rc) return rc;
+  return epsb_expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, excl, gemm_map, scratch,
+                           scale_map, red_map, ret_incl, stream);
 }
 
 extern "C" int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, int32_t* excl, int32_t* mapping,

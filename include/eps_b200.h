@@ -109,6 +109,28 @@ int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int 
                       int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm,
                       int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, void* stream);
 
+/* Same plans as epsb_expert_plans, for callers that are not allowed to allocate device memory.
+ * This entry point has no counterpart in the reference.
+ *
+ * Who needs it: a host that was handed all of its buffers up front and must not call the allocator while it runs —
+ * for example a serving loop whose memory is planned once per model (a cudaMalloc there would stall every stream of
+ * the device), or a plug-in loaded by a runtime that owns the arena and gives the plug-in no allocation hook.  Such a
+ * caller can provide the outputs but has nowhere to get the kernel's private scratch (the inverse GEMM map) from.
+ *
+ * Here that scratch is a fixed array inside the library's device image: 2^20 int32 entries (4 MiB), held by every GPU
+ * that loads the library until the process exits.  Limits and rules:
+ *   - max_rows * k must be <= 1048576, otherwise EPSB_ERR_WORKSPACE is returned and nothing is launched;
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
+ *     current) and remembers it; make that first call before any stream capture begins;
+ *   - every call on a device shares the one array: two calls whose kernels overlap on the GPU (different streams)
+ *     race on it.  Nothing in it has to start at zero — the kernel writes every entry it later reads — and after
+ *     the call it simply holds the last call's inverse map.
+ * Arguments are those of epsb_expert_plans without inv_gemm. */
+int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
+                              int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map,
+                              int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, void* stream);
+
 /* ----------------------------------------------------------------------------
  * fast_ep plans.  ref: src/fast_ep/all_to_all/fast_ep_kernels.cu:40-176
  * (expandPlan) and :352-610 (allGatherPlan + planKernel).
