@@ -37,6 +37,34 @@ def _excl(incl: np.ndarray) -> np.ndarray:
     return out
 
 
+def dispatch_windows(gathered: np.ndarray, rank: int, W: int, S: int):
+    """Host view of one exchange from the all-gathered inclusive send plans `gathered[W, W*S]`:
+    (send_excl, send_incl, recv_excl, recv_incl) as int64 arrays of W*S entries, rows counted in this rank's send
+    order and receive order (source-major, then stage — reference alltoall_runner.cu:60-101)."""
+    g = np.asarray(gathered, dtype=np.int64).reshape(W, W * S)
+    send_incl = g[rank]
+    counts = np.zeros((W, S), dtype=np.int64)  # rows rank r sends me at stage s
+    for r in range(W):
+        for s in range(S):
+            i = rank * S + s
+            counts[r, s] = g[r, i] - (g[r, i - 1] if i > 0 else 0)
+    recv_incl = np.cumsum(counts.reshape(-1))
+    return _excl(send_incl), send_incl, _excl(recv_incl), recv_incl
+
+
+def stage_slices(windows, W: int, S: int, stage: int):
+    """Per peer p: ((send_begin, send_end), (recv_begin, recv_end)) row ranges of one stage (stage < 0: all stages)."""
+    s_ex, s_in, r_ex, r_in = windows
+    out = []
+    for p in range(W):
+        if stage < 0:
+            out.append(((int(s_ex[p * S]), int(s_in[p * S + S - 1])), (int(r_ex[p * S]), int(r_in[p * S + S - 1]))))
+        else:
+            i = p * S + stage
+            out.append(((int(s_ex[i]), int(s_in[i])), (int(r_ex[i]), int(r_in[i]))))
+    return out
+
+
 class Scheduler:
     def __init__(self, top_k: int, num_experts: int, hidden_size: int, input_scales_dim: int,
                  max_num_tokens_per_gpu: int, comm: Communicator | None, local_num_experts: int,
@@ -116,17 +144,8 @@ class Scheduler:
             gathered = self.comm.all_gather(ctx.send_incl)               # [W, W*S] on the device
             ctx.recv_incl, ctx.remote_offset = ops.recv_plan(gathered, self.rank, W, S)
             g = gathered.cpu().numpy()                                   # the one host read of the rendezvous
-            send_incl = g[self.rank]
-            counts = np.zeros((W, S), dtype=np.int64)                    # rows rank r sends me at stage s
-            for r in range(W):
-                row = g[r]
-                for s in range(S):
-                    i = self.rank * S + s
-                    counts[r, s] = row[i] - (row[i - 1] if i > 0 else 0)
-            recv_incl = np.cumsum(counts.reshape(-1)).astype(np.int64)
-            ctx.host_dispatch = (_excl(send_incl.astype(np.int64)), send_incl.astype(np.int64), _excl(recv_incl),
-                                 recv_incl)
-            ctx.n_recv = int(recv_incl[-1])
+            ctx.host_dispatch = dispatch_windows(g, self.rank, W, S)
+            ctx.n_recv = int(ctx.host_dispatch[3][-1])
             rows_bound = ctx.n_recv
             if ctx.n_recv > self.arena_rows:
                 raise EpsError("received rows exceed the arena")
@@ -156,18 +175,8 @@ class Scheduler:
         if self.W == 1:
             return  # recv aliases send
         W, S = self.W, ctx.num_stages
-        s_ex, s_in, r_ex, r_in = ctx.host_combine if combine else ctx.host_dispatch
-        sends, recvs = [None] * W, [None] * W
-        for p in range(W):
-            if stage < 0:
-                a, b = s_ex[p * S], s_in[p * S + S - 1]
-                c, d = r_ex[p * S], r_in[p * S + S - 1]
-            else:
-                a, b = s_ex[p * S + stage], s_in[p * S + stage]
-                c, d = r_ex[p * S + stage], r_in[p * S + stage]
-            sends[p] = send[a:b]
-            recvs[p] = recv[c:d]
-        self.comm.exchange(sends, recvs)
+        sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, W, S, stage)
+        self.comm.exchange([send[a:b] for (a, b), _ in sl], [recv[c:d] for _, (c, d) in sl])
 
     def prologue(self, expert_scales: torch.Tensor, hidden_states: torch.Tensor, input_scales=None,
                  recv_input_scales=None, raw_input: torch.Tensor | None = None) -> None:
