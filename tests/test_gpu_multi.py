@@ -91,3 +91,78 @@ def test_layer_ep2_vs_oracle(case):
         p.join(timeout=60)
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def _fastep_worker(rank, world, port, q):
+    try:
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        import torch.distributed as dist
+
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from helpers import random_routing
+        from oracle import oracle as orc
+
+        from eps_b200.communication import Communicator, CommunicatorParams
+        from eps_b200.fast_ep import AllToAll
+
+        T, k, E, H = 90 + 11 * rank, 4, 16, 1024
+        EL = E // world
+        rng = np.random.default_rng(50 + rank)
+        idx, w = random_routing(rng, T, k, E, 3)
+        x = torch.randn((T, H), generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16)
+        comm = Communicator(None, CommunicatorParams(rank, world, world))
+        a2a = AllToAll(k, E, H, 256, comm)
+        excl = torch.empty((EL + 1,), dtype=torch.int32, device=dev)
+        expert_x = torch.zeros((256 * k, H), dtype=torch.bfloat16, device=dev)
+        a2a.dispatch(excl, expert_x, x.to(dev), torch.from_numpy(idx).to(dev), 256)
+        ex = excl.cpu().numpy()
+        y = torch.zeros_like(expert_x)
+        for le in range(EL):   # expert e scales its rows by (1 + e/8)
+            e = rank * EL + le
+            y[ex[le]:ex[le + 1]] = (expert_x[ex[le]:ex[le + 1]].float() * (1 + e / 8)).to(torch.bfloat16)
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        a2a.combine(out, torch.from_numpy(w).to(dev), y, 256)
+        torch.cuda.synchronize()
+        _, rmap = orc.fastep_expand_plan(idx, E)
+        rows = torch.zeros((T * k, H), dtype=torch.bfloat16)
+        for i in range(T * k):
+            if rmap[i] < 1000000:
+                rows[rmap[i]] = (x[i // k].float() * (1 + idx.reshape(-1)[i] / 8)).to(torch.bfloat16)
+        b = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+        want = orc.fastep_reduce(b(rows), b(x), w, rmap)
+        ok = np.array_equal(b(out), want)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok" if ok else "fast_ep output differs from the oracle"))
+    except Exception:
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+def test_fastep_ep2_bit_exact():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from eps_b200 import build
+    from oracle import oracle as orc
+
+    build.build()
+    orc.build()
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 1000
+    procs = [ctx.Process(target=_fastep_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
