@@ -125,6 +125,61 @@ class MoELayerFP8:
         self.kernel_launches = n
         return out
 
+    # ------------------------------------------------------------------ host-buffer entry point
+
+    def _host_pipeline(self):
+        if getattr(self, "_hp", None) is None:
+            T, H, k = max(self.max_tok, 1), self.H, self.k
+            dev = self.dev
+            self._hp = dict(
+                h2d=torch.cuda.Stream(device=dev), d2h=torch.cuda.Stream(device=dev), slot=0,
+                x=[torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                idx=[torch.empty((T, k), dtype=torch.int32, device=dev) for _ in range(2)],
+                w=[torch.empty((T, k), dtype=torch.float32, device=dev) for _ in range(2)],
+                out=[torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                in_ready=[torch.cuda.Event() for _ in range(2)], in_free=[None, None],
+                out_ready=[torch.cuda.Event() for _ in range(2)], out_free=[None, None])
+        return self._hp
+
+    def forward_host(self, x_host: torch.Tensor, idx_host: torch.Tensor, w_host: torch.Tensor,
+                     out_host: torch.Tensor, num_global_tokens: int | None = None) -> None:
+        """Same layer for HOST (pinned) tensors.  Asynchronous: the inputs are copied to one of two device slots on a
+        copy stream, the layer runs on the current stream, the result is copied into `out_host` on a second copy
+        stream; consecutive calls overlap (copy-in of call i+1 and copy-out of call i-1 with the compute of call i).
+        Call `synchronize_host()` before reading `out_host`."""
+        hp = self._host_pipeline()
+        T = x_host.shape[0]
+        i = hp["slot"]
+        hp["slot"] = 1 - i
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(hp["h2d"]):
+            if hp["in_free"][i] is not None:
+                hp["h2d"].wait_event(hp["in_free"][i])     # the call that last used this slot has consumed it
+            hp["idx"][i][:T].copy_(idx_host, non_blocking=True)
+            hp["w"][i][:T].copy_(w_host, non_blocking=True)
+            hp["x"][i][:T].copy_(x_host, non_blocking=True)
+            hp["in_ready"][i].record(hp["h2d"])
+        main.wait_event(hp["in_ready"][i])
+        if hp["out_free"][i] is not None:
+            main.wait_event(hp["out_free"][i])             # the previous result in this slot has left the device
+        self.forward(hp["x"][i][:T], hp["idx"][i][:T], hp["w"][i][:T], num_global_tokens, out=hp["out"][i][:T])
+        done = torch.cuda.Event()
+        done.record(main)
+        hp["in_free"][i] = done
+        hp["out_ready"][i].record(main)
+        with torch.cuda.stream(hp["d2h"]):
+            hp["d2h"].wait_event(hp["out_ready"][i])
+            out_host.copy_(hp["out"][i][:T], non_blocking=True)
+            free = torch.cuda.Event()
+            free.record(hp["d2h"])
+            hp["out_free"][i] = free
+
+    def synchronize_host(self) -> None:
+        hp = self._host_pipeline()
+        hp["h2d"].synchronize()
+        torch.cuda.current_stream().synchronize()
+        hp["d2h"].synchronize()
+
     def check_status(self) -> None:
         """Raises if a bounded device-side wait of a GEMM kernel expired (synchronises)."""
         st = self.status.cpu().tolist()

@@ -117,3 +117,29 @@ def test_scheduler_reference_flow_bf16(cuda, oracle):
     assert np.max(np.abs(got - want)) <= 3e-2 * np.abs(want).max()
     with pytest.raises(Exception, match="Invalid num_stages"):
         sched.rendezvous_and_plan(d_idx, d_w, T, 3, False)
+
+
+def test_forward_host_matches_forward(cuda, oracle):
+    """The pinned-host entry point (double-buffered copies on side streams) returns the same bits as the resident
+    call, for several back-to-back calls with different inputs."""
+    from eps_b200 import workloads
+    from eps_b200.layer import MoELayerFP8
+
+    T, H, I, E, k = 96, 512, 256, 8, 2
+    cfg = workloads.CONFIGS[0].scaled(tokens_per_rank=T, hidden=H, inter=I, num_experts=E, top_k=k)
+    dev_w, _ = _weights(cfg, range(E), cuda, oracle)
+    layer = MoELayerFP8(H, I, E, k, T, *dev_w)
+    outs_h, wants = [], []
+    for step in range(5):
+        c = cfg.scaled(cfg_id=10 + step)
+        x = workloads.make_tokens(c).pin_memory()
+        idx, w = workloads.make_routing(c)
+        idx, w = idx.pin_memory(), w.pin_memory()
+        o = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+        layer.forward_host(x, idx, w, o)
+        outs_h.append(o)
+        wants.append((x, idx, w))
+    layer.synchronize_host()
+    for o, (x, idx, w) in zip(outs_h, wants):
+        ref = layer.forward(x.to(cuda), idx.to(cuda), w.to(cuda))
+        assert torch.equal(o, ref.cpu())
