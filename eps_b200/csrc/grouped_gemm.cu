@@ -10,7 +10,7 @@
 //     ragged tile list built on the device from the expert prefix sum;
 //   * tile = 128 rows (tokens) x 256 weight rows, K step 128 (= one 128-byte
 //     swizzle atom of e4m3, four tcgen05.mma of K=32);
-//   * warp 0 issues TMA loads into a 4-stage shared-memory ring, warp 1 issues
+//   * warp 0 issues TMA loads into a 3-stage shared-memory ring, warp 1 issues
 //     the MMAs into one of two 256-column TMEM buffers, warps 4..11 (two
 //     warpgroups) drain a TMEM buffer per K step with tcgen05.ld and fold it
 //     into fp32 register accumulators multiplied by a_scale[row,kb]*b_scale[nb,kb]
@@ -31,7 +31,8 @@ namespace {
 constexpr int kBM = 128;           // rows per tile
 constexpr int kBN = 256;           // weight rows per tile (two 128-row TMA boxes)
 constexpr int kBK = 128;           // K step (bytes == elements for e4m3)
-constexpr int kStages = 4;
+constexpr int kStages = 3;           // 3 vs 4 stages measure the same; the fourth stage's room stages the tile output
+constexpr int kOutRowBytes = 256 + 16;  // one thread's 128 bf16 (or 64 codes) + padding against bank conflicts
 constexpr int kABytes = kBM * kBK;         // 16 KB
 constexpr int kBBytes = kBN * kBK;         // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -50,6 +51,7 @@ constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
 struct SharedStorage {
   // tile ring first: every stage base must be 1024-byte aligned for the 128-byte swizzle
   uint8_t tiles[kStages][kStageBytes];
+  uint8_t out_stage[2][kBM][kOutRowBytes];  // [column half][row]: tile output on its way to global memory
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[2];
@@ -169,6 +171,20 @@ __device__ __forceinline__ void tmem_tie(uint32_t (&r)[32]) {
                  "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
                  "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                :
+               : "memory");
+}
+
+// One row of the staged tile output -> global memory, asynchronously (bulk copy engine).  dst, src 16-byte aligned.
+__device__ __forceinline__ void bulk_store_row(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// The staging rows written by this thread's earlier bulk copies may be overwritten again.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_16(void* p, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 
@@ -413,7 +429,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
         for (int i = 0; i < 64; i++) {
           const float g = acc[i], u = acc[64 + i];
-          const float a = (g / (1.0f + __expf(-g))) * u;
+          const float a = (g * __frcp_rn(1.0f + __expf(-g))) * u;  // silu(g) * u; checked by tolerance, not bit-exact
           acc[i] = a;
           amax = fmaxf(amax, fabsf(a));
         }
@@ -426,8 +442,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         amax_phase ^= 1;
         const float scale = __fdiv_rn(amax, kFp8Max);
         const float inv = __frcp_rn(scale);
+        uint8_t* stage_row = sm->out_stage[half][r_in_tile];
+        bulk_wait_read();  // this thread's copy of the previous tile has left the staging row
         if (row_ok) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + grow * I + (int64_t)c.n * 128 + 64 * half;
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) {
             uint32_t w[4];
@@ -437,18 +454,25 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
               w[j] = (uint32_t)cvt_e4m3x2(quant_clamp(acc[i], inv), quant_clamp(acc[i + 1], inv)) |
                      ((uint32_t)cvt_e4m3x2(quant_clamp(acc[i + 2], inv), quant_clamp(acc[i + 3], inv)) << 16);
             }
-            st_16(dst + q4 * 16, make_uint4(w[0], w[1], w[2], w[3]));
+            st_shared_16(stage_row + q4 * 16, make_uint4(w[0], w[1], w[2], w[3]));
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          bulk_store_row(reinterpret_cast<uint8_t*>(p.C) + grow * I + (int64_t)c.n * 128 + 64 * half, stage_row, 64);
+          bulk_commit();
           if (half == 0) p.c_s[grow * (I / 128) + c.n] = scale;
         }
         // amax_x alternates between two copies: a copy is rewritten two tiles later, and a thread
         // cannot pass the next tile's amax_bar before its partner has arrived there, i.e. has read.
       } else {
         const int64_t col0 = (int64_t)c.n * kBN + 128 * half;
+        uint8_t* stage_row = sm->out_stage[half][r_in_tile];
+        bulk_wait_read();  // this thread's copy of the previous tile has left the staging row
         if (row_ok && col0 < p.N) {
           float wgt = 1.0f;
           if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr) wgt = __ldg(p.row_w + grow);
-          uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + (grow * p.N + col0) * 2;
+          // The thread's 256 bytes go to its own padded row of shared memory (16-byte stores of a warp land in
+          // distinct banks) and leave for global memory as ONE asynchronous 256-byte bulk copy, instead of sixteen
+          // scattered 16-byte stores per thread; the copy overlaps the next tile's K loop.
 #pragma unroll
           for (int q8 = 0; q8 < 16; q8++) {
             uint4 o;
@@ -456,11 +480,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             o.y = pack_bf16x2(acc[q8 * 8 + 2] * wgt, acc[q8 * 8 + 3] * wgt);
             o.z = pack_bf16x2(acc[q8 * 8 + 4] * wgt, acc[q8 * 8 + 5] * wgt);
             o.w = pack_bf16x2(acc[q8 * 8 + 6] * wgt, acc[q8 * 8 + 7] * wgt);
-            st_16(dst + q8 * 16, o);
+            st_shared_16(stage_row + q8 * 16, o);
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          bulk_store_row(reinterpret_cast<uint8_t*>(p.C) + (grow * p.N + col0) * 2, stage_row, 256);
+          bulk_commit();
         }
       }
     }
+    bulk_wait_all();  // every staged row has reached global memory before the CTA's shared memory goes away
   }
 
   // ---- teardown

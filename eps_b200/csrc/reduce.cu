@@ -169,13 +169,14 @@ reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red
         if (j < k && rows[j] >= 0) in[j] = ld_nc_16(y + (int64_t)rows[j] * row_bytes + (int64_t)v * 16);
       uint4 sh = make_uint4(0, 0, 0, 0), xin = make_uint4(0, 0, 0, 0);
       if (shared != nullptr) sh = ld_nc_16(shared + off);
-      if (zero_scale != nullptr) xin = ld_nc_16(x + off);
+      const bool has_zero = zero_scale != nullptr && zs != 0.0f;  // tokens without identity experts skip the x row
+      if (has_zero) xin = ld_nc_16(x + off);
       float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int j = 0; j < kMaxSlots; j++)
         if (j < k && rows[j] >= 0) acc_f32(a, in[j]);
       if (shared != nullptr) acc_f32(a, sh);
-      if (zero_scale != nullptr) fma_f32(a, xin, zs);
+      if (has_zero) fma_f32(a, xin, zs);
       st_16(out + off, pack8(a));
     }
   }
