@@ -31,8 +31,14 @@ namespace {
 constexpr int kBM = 128;           // rows per tile
 constexpr int kBN = 256;           // weight rows per tile (two 128-row TMA boxes)
 constexpr int kBK = 128;           // K step (bytes == elements for e4m3)
-constexpr int kStages = 3;           // 3 vs 4 stages measure the same; the fourth stage's room stages the tile output
-constexpr int kOutRowBytes = 256 + 16;  // one thread's 128 bf16 (or 64 codes) + padding against bank conflicts
+// Shared memory is split between the TMA ring and the staging rows of the tile output.  Gate/up stores 64 bytes per
+// thread and keeps four stages (measured: 5.6 vs 5.2 TB/s of weight streaming at 128 rows per expert); the bf16 modes
+// store 256 bytes per thread and keep three (their output staging is worth more than the fourth stage).
+template <int kMode>
+struct ModeCfg {
+  static constexpr int kStages = kMode == EPSB_GEMM_GATEUP ? 4 : 3;
+  static constexpr int kOutRowBytes = (kMode == EPSB_GEMM_GATEUP ? 64 : 256) + 16;  // + padding against bank conflicts
+};
 constexpr int kABytes = kBM * kBK;         // 16 KB
 constexpr int kBBytes = kBN * kBK;         // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -48,7 +54,10 @@ constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_
 // descriptor version 1 (bits 46-47), layout SWIZZLE_128B = 2 (bits 61-63).
 constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
 
+template <int kMode>
 struct SharedStorage {
+  static constexpr int kStages = ModeCfg<kMode>::kStages;
+  static constexpr int kOutRowBytes = ModeCfg<kMode>::kOutRowBytes;
   // tile ring first: every stage base must be 1024-byte aligned for the 128-byte swizzle
   uint8_t tiles[kStages][kStageBytes];
   uint8_t out_stage[2][kBM][kOutRowBytes];  // [column half][row]: tile output on its way to global memory
@@ -92,7 +101,8 @@ __device__ __forceinline__ uint64_t global_ns() {
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, SharedStorage* sm, int32_t* status, int code) {
+template <class Storage>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Storage* sm, int32_t* status, int code) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
@@ -207,7 +217,8 @@ struct TileCoord {
   int e, row0, rows_left, n;  // expert, first GEMM row of the tile, valid rows from row0, n-tile index
 };
 
-__device__ __forceinline__ TileCoord locate_tile(int t, const GemmParams& p, const SharedStorage* sm) {
+template <class Storage>
+__device__ __forceinline__ TileCoord locate_tile(int t, const GemmParams& p, const Storage* sm) {
   const int g = t / p.n_tiles;
   TileCoord c;
   c.n = t - g * p.n_tiles;
@@ -230,7 +241,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  SharedStorage* sm = reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  using Storage = SharedStorage<kMode>;
+  constexpr int kStages = Storage::kStages;
+  Storage* sm = reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (int)(p.K / kBK);
 
@@ -535,7 +548,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K) {
 
 template <int kMode>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
-  const size_t smem = sizeof(SharedStorage) + 1024;
+  const size_t smem = sizeof(SharedStorage<kMode>) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
