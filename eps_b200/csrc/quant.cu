@@ -15,26 +15,43 @@ namespace {
 constexpr int kQuantThreads = 256;
 constexpr int kUnroll = 4;  // groups in flight per half-warp
 
+// |a| and max on packed bf16 pairs (exact: bf16 abs/max involve no rounding; a NaN operand is dropped like
+// the reference's std::max(absmax, fabs(v)) drops it).
+__device__ __forceinline__ uint32_t habs2_u32(uint32_t a) { return a & 0x7fff7fffu; }
+__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 template <bool kDivFull>
 __device__ __forceinline__ void quant_group_store(uint4 v, int sub, bool live, uint8_t* qdst, float* sdst) {
-  float f[8];
-  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
-  f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
-  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
-  f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(f[i]));
+  // amax of the lane's 8 values on packed pairs, then one conversion to fp32
+  uint32_t m = hmax2_u32(hmax2_u32(habs2_u32(v.x), habs2_u32(v.y)), hmax2_u32(habs2_u32(v.z), habs2_u32(v.w)));
+  float amax = fmaxf(bf16_lo(m), bf16_hi(m));
   // 16-lane butterfly; xor offsets < 16 never cross the half-warp.
 #pragma unroll
   for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
   const float scale = scale_of_amax<kDivFull>(amax);
   const float inv = __frcp_rn(scale);
+  float f[8];
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+  f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+  f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
   uint2 out;
-  out.x = (uint32_t)cvt_e4m3x2(quant_clamp(f[0], inv), quant_clamp(f[1], inv)) |
-          ((uint32_t)cvt_e4m3x2(quant_clamp(f[2], inv), quant_clamp(f[3], inv)) << 16);
-  out.y = (uint32_t)cvt_e4m3x2(quant_clamp(f[4], inv), quant_clamp(f[5], inv)) |
-          ((uint32_t)cvt_e4m3x2(quant_clamp(f[6], inv), quant_clamp(f[7], inv)) << 16);
+  if (inv <= 3.0e38f) {
+    // Finite reciprocal: |x * inv| <= 448 * (1 + a few ulp), and everything in [448, 464) rounds to 448 while the
+    // conversion saturates above, so the reference's explicit clamp to +-448 cannot change a code here.
+    out.x = (uint32_t)cvt_e4m3x2(f[0] * inv, f[1] * inv) | ((uint32_t)cvt_e4m3x2(f[2] * inv, f[3] * inv) << 16);
+    out.y = (uint32_t)cvt_e4m3x2(f[4] * inv, f[5] * inv) | ((uint32_t)cvt_e4m3x2(f[6] * inv, f[7] * inv) << 16);
+  } else {
+    // scale 0 or denormal: 0 * inf = NaN, which the reference's fmin/fmax turn into +448; keep its exact sequence
+    out.x = (uint32_t)cvt_e4m3x2(quant_clamp(f[0], inv), quant_clamp(f[1], inv)) |
+            ((uint32_t)cvt_e4m3x2(quant_clamp(f[2], inv), quant_clamp(f[3], inv)) << 16);
+    out.y = (uint32_t)cvt_e4m3x2(quant_clamp(f[4], inv), quant_clamp(f[5], inv)) |
+            ((uint32_t)cvt_e4m3x2(quant_clamp(f[6], inv), quant_clamp(f[7], inv)) << 16);
+  }
   if (live) {
     *reinterpret_cast<uint2*>(qdst + sub * 8) = out;
     if (sub == 0) *sdst = scale;
@@ -59,17 +76,19 @@ quant_1x128_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, floa
   const int64_t wid = ((int64_t)blockIdx.x * kQuantThreads + threadIdx.x) >> 5;
   const int64_t n_w = ((int64_t)gridDim.x * kQuantThreads) >> 5;
   const int64_t base = row0 * groups_per_row;
-  for (int64_t p0 = wid; p0 < n_pairs; p0 += n_w * kUnroll) {
+  // a warp's kUnroll pairs are adjacent (2 KB contiguous per warp per step): measured 5.9 TB/s vs 4.7 TB/s
+  // when the unrolled pairs were a grid stride apart
+  for (int64_t p0 = wid * kUnroll; p0 < n_pairs; p0 += n_w * kUnroll) {
     uint4 v[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
-      const int64_t t = 2 * (p0 + (int64_t)u * n_w) + half;
+      const int64_t t = 2 * (p0 + u) + half;
       v[u] = make_uint4(0, 0, 0, 0);
       if (t < n_tasks) v[u] = ld_nc_16(x + (base + t) * 128 + sub * 8);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
-      const int64_t p = p0 + (int64_t)u * n_w;
+      const int64_t p = p0 + u;
       if (p < n_pairs) {  // warp-uniform: the shuffles inside need all 32 lanes
         const int64_t t = 2 * p + half;
         quant_group_store<kDivFull>(v[u], sub, t < n_tasks, q + (base + t) * 128, scales + base + t);

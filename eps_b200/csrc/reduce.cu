@@ -13,7 +13,8 @@ namespace {
 
 constexpr int kRedThreads = 256;
 constexpr int kRedWarps = kRedThreads / 32;
-constexpr int kMaxSlots = 16;  // top-k / world size held in registers per vector
+constexpr int kMaxSlots = 16;  // largest top-k / world size a register-resident kernel takes
+// Kernels are instantiated for 4, 8, 12 and 16 summands: fewer registers -> more resident warps -> more loads in flight.
 
 union BfVec {
   uint4 u;
@@ -64,7 +65,7 @@ struct StageWindows {
 
 // ---------------------------------------------------------------- local reduce (expert rank)
 
-template <bool kRefArith>
+template <bool kRefArith, int kSlots>
 __global__ void __launch_bounds__(kRedThreads)
 local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_recv,
                     const int32_t* __restrict__ scale_map, const int32_t* __restrict__ red_map, StageWindows win,
@@ -81,10 +82,10 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
     win.window(d, b, e);
     const int64_t first = (warp - seen % n_warps + n_warps) % n_warps;
     for (int64_t q = b + first; q < e; q += n_warps) {
-      int32_t rows[kMaxSlots];
-      float wts[kMaxSlots];
+      int32_t rows[kSlots];
+      float wts[kSlots];
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++) {
+      for (int j = 0; j < kSlots; j++) {
         rows[j] = -1;
         wts[j] = 0.0f;
         if (j < k) {
@@ -96,9 +97,9 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
         }
       }
       for (int v = lane; v < vecs; v += 32) {
-        uint4 in[kMaxSlots];
+        uint4 in[kSlots];
 #pragma unroll
-        for (int j = 0; j < kMaxSlots; j++)
+        for (int j = 0; j < kSlots; j++)
           if (j < k && rows[j] >= 0) in[j] = ld_nc_16(y + (int64_t)rows[j] * row_bytes + (int64_t)v * 16);
         uint4 out;
         if constexpr (kRefArith) {
@@ -107,7 +108,7 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
           BfVec acc;
           acc.u = make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int j = 0; j < kMaxSlots; j++)
+          for (int j = 0; j < kSlots; j++)
             if (j < k && rows[j] >= 0) {
               BfVec t;
               t.u = in[j];
@@ -122,7 +123,7 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
         } else {
           float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-          for (int j = 0; j < kMaxSlots; j++)
+          for (int j = 0; j < kSlots; j++)
             if (j < k && rows[j] >= 0) acc_f32(a, in[j]);
           out = pack8(a);
         }
@@ -138,6 +139,7 @@ local_reduce_kernel(const uint8_t* __restrict__ y, const float* __restrict__ w_r
 // out[t,:] = bf16( sum_j float(y[red_map[q,j],:]) + shared[t,:] + x[t,:] * zero_scale[t] ), q = glob_map[t]
 // (the return row of token t; with one rank the return buffer IS the collect buffer).  fp32 accumulation in
 // slot order, one rounding.  Replaces local_reduce -> (no-op exchange) -> global_reduce for ep_world_size 1.
+template <int kSlots>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red_map,
                   const int32_t* __restrict__ glob_map, const int32_t* __restrict__ ret_incl, int S,
@@ -151,9 +153,9 @@ reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red
   const int64_t sentinel = (int64_t)ret_incl[S - 1] * k;
   for (int64_t t = warp; t < T; t += n_warps) {
     const int32_t q = __ldg(glob_map + t);
-    int32_t rows[kMaxSlots];
+    int32_t rows[kSlots];
 #pragma unroll
-    for (int j = 0; j < kMaxSlots; j++) {
+    for (int j = 0; j < kSlots; j++) {
       rows[j] = -1;
       if (j < k && q < T) {
         const int32_t r = __ldg(red_map + (int64_t)q * k + j);
@@ -163,9 +165,9 @@ reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red
     const float zs = zero_scale != nullptr ? __ldg(zero_scale + t) : 0.0f;
     for (int v = lane; v < vecs; v += 32) {
       const int64_t off = t * row_bytes + (int64_t)v * 16;
-      uint4 in[kMaxSlots];
+      uint4 in[kSlots];
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++)
+      for (int j = 0; j < kSlots; j++)
         if (j < k && rows[j] >= 0) in[j] = ld_nc_16(y + (int64_t)rows[j] * row_bytes + (int64_t)v * 16);
       uint4 sh = make_uint4(0, 0, 0, 0), xin = make_uint4(0, 0, 0, 0);
       if (shared != nullptr) sh = ld_nc_16(shared + off);
@@ -173,7 +175,7 @@ reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red
       if (has_zero) xin = ld_nc_16(x + off);
       float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++)
+      for (int j = 0; j < kSlots; j++)
         if (j < k && rows[j] >= 0) acc_f32(a, in[j]);
       if (shared != nullptr) acc_f32(a, sh);
       if (has_zero) fma_f32(a, xin, zs);
@@ -184,7 +186,7 @@ reduce_ep1_kernel(const uint8_t* __restrict__ y, const int32_t* __restrict__ red
 
 // ---------------------------------------------------------------- global reduce (source rank)
 
-template <bool kRefArith>
+template <bool kRefArith, int kSlots>
 __global__ void __launch_bounds__(kRedThreads)
 global_reduce_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict__ glob_map,
                      const uint8_t* __restrict__ shared, const uint8_t* __restrict__ x,
@@ -196,9 +198,9 @@ global_reduce_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict
   const int64_t row_bytes = H * 2;
   const int32_t sentinel = T * W;
   for (int64_t t = warp; t < T; t += n_warps) {
-    int32_t rows[kMaxSlots];
+    int32_t rows[kSlots];
 #pragma unroll
-    for (int j = 0; j < kMaxSlots; j++) {
+    for (int j = 0; j < kSlots; j++) {
       rows[j] = -1;
       if (j < W) {
         const int32_t r = __ldg(glob_map + t * W + j);
@@ -208,9 +210,9 @@ global_reduce_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict
     const float zs = zero_scale != nullptr ? __ldg(zero_scale + t) : 0.0f;
     for (int v = lane; v < vecs; v += 32) {
       const int64_t off = t * row_bytes + (int64_t)v * 16;
-      uint4 in[kMaxSlots];
+      uint4 in[kSlots];
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++)
+      for (int j = 0; j < kSlots; j++)
         if (j < W && rows[j] >= 0) in[j] = ld_nc_16(recv + (int64_t)rows[j] * row_bytes + (int64_t)v * 16);
       uint4 sh = make_uint4(0, 0, 0, 0), xin = make_uint4(0, 0, 0, 0);
       if (shared != nullptr) sh = ld_nc_16(shared + off);
@@ -222,7 +224,7 @@ global_reduce_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict
         BfVec acc;
         acc.u = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int j = 0; j < kMaxSlots; j++)
+        for (int j = 0; j < kSlots; j++)
           if (j < W && rows[j] >= 0) {
             BfVec tv;
             tv.u = in[j];
@@ -248,7 +250,7 @@ global_reduce_kernel(const uint8_t* __restrict__ recv, const int32_t* __restrict
       } else {
         float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-        for (int j = 0; j < kMaxSlots; j++)
+        for (int j = 0; j < kSlots; j++)
           if (j < W && rows[j] >= 0) acc_f32(a, in[j]);
         if (shared != nullptr) acc_f32(a, sh);
         if (zero_scale != nullptr) fma_f32(a, xin, zs);
@@ -320,6 +322,7 @@ global_reduce_wide_kernel(const uint8_t* __restrict__ recv, const int32_t* __res
 
 // ---------------------------------------------------------------- fast_ep combine
 
+template <int kSlots>
 __global__ void __launch_bounds__(kRedThreads)
 fastep_reduce_kernel(const uint8_t* __restrict__ rows_in, const uint8_t* __restrict__ raw,
                      const uint8_t* __restrict__ shared, const float* __restrict__ w,
@@ -330,10 +333,10 @@ fastep_reduce_kernel(const uint8_t* __restrict__ rows_in, const uint8_t* __restr
   const int vecs = (int)(H >> 3);
   const int64_t row_bytes = H * 2;
   for (int64_t t = warp; t < T; t += n_warps) {
-    const uint8_t* srcs[kMaxSlots];
-    float wts[kMaxSlots];
+    const uint8_t* srcs[kSlots];
+    float wts[kSlots];
 #pragma unroll
-    for (int j = 0; j < kMaxSlots; j++) {
+    for (int j = 0; j < kSlots; j++) {
       srcs[j] = nullptr;
       wts[j] = 0.0f;
       if (j < k) {
@@ -343,13 +346,13 @@ fastep_reduce_kernel(const uint8_t* __restrict__ rows_in, const uint8_t* __restr
       }
     }
     for (int v = lane; v < vecs; v += 32) {
-      uint4 in[kMaxSlots];
+      uint4 in[kSlots];
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++)
+      for (int j = 0; j < kSlots; j++)
         if (j < k) in[j] = ld_nc_16(srcs[j] + (int64_t)v * 16);
       float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-      for (int j = 0; j < kMaxSlots; j++)
+      for (int j = 0; j < kSlots; j++)
         if (j < k) fma_f32(a, in[j], wts[j]);
       const int64_t off = t * row_bytes + (int64_t)v * 16;
       if (shared != nullptr) acc_f32(a, ld_nc_16(shared + off));
@@ -392,6 +395,15 @@ silu_kernel(const uint8_t* __restrict__ gate_up, uint8_t* __restrict__ act, cons
   }
 }
 
+// Picks the instantiation with the smallest slot capacity >= n.
+#define EPSB_SLOT_SWITCH(n, ...)            \
+  do {                                      \
+    if ((n) <= 4) { constexpr int kS = 4; __VA_ARGS__; }        \
+    else if ((n) <= 8) { constexpr int kS = 8; __VA_ARGS__; }   \
+    else if ((n) <= 12) { constexpr int kS = 12; __VA_ARGS__; } \
+    else { constexpr int kS = 16; __VA_ARGS__; }                \
+  } while (0)
+
 int red_grid(int64_t rows) {
   int64_t want = (rows + kRedWarps - 1) / kRedWarps;
   const int64_t cap = (int64_t)sm_count() * 8;
@@ -420,8 +432,8 @@ extern "C" int epsb_local_reduce_ref(const void* y, const float* w_recv, const i
   EPSB_REQUIRE(stage >= -1 && stage < S, EPSB_ERR_INVALID, "stage %d out of range for %d stages", stage, S);
   if (max_rows <= 0) return EPSB_OK;
   StageWindows win{ret_incl, W, S, stage};
-  local_reduce_kernel<true><<<red_grid(max_rows), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const uint8_t*)y, w_recv, scale_map, red_map, win, k, H, (uint8_t*)send);
+  EPSB_SLOT_SWITCH(k, (local_reduce_kernel<true, kS><<<red_grid(max_rows), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)y, w_recv, scale_map, red_map, win, k, H, (uint8_t*)send)));
   return check_launch("local_reduce_ref");
 }
 
@@ -433,8 +445,8 @@ extern "C" int epsb_local_reduce(const void* y, const int32_t* red_map, const in
   EPSB_REQUIRE(stage >= -1 && stage < S, EPSB_ERR_INVALID, "stage %d out of range for %d stages", stage, S);
   if (max_rows <= 0) return EPSB_OK;
   StageWindows win{ret_incl, W, S, stage};
-  local_reduce_kernel<false><<<red_grid(max_rows), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const uint8_t*)y, nullptr, nullptr, red_map, win, k, H, (uint8_t*)send);
+  EPSB_SLOT_SWITCH(k, (local_reduce_kernel<false, kS><<<red_grid(max_rows), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)y, nullptr, nullptr, red_map, win, k, H, (uint8_t*)send)));
   return check_launch("local_reduce");
 }
 
@@ -448,9 +460,8 @@ static int launch_global_reduce(const void* recv, const int32_t* glob_map, const
   if (T <= 0) return EPSB_OK;
   auto st = static_cast<cudaStream_t>(stream);
   if (W <= kMaxSlots)
-    global_reduce_kernel<kRef><<<red_grid(T), kRedThreads, 0, st>>>((const uint8_t*)recv, glob_map,
-                                                                    (const uint8_t*)shared, (const uint8_t*)x,
-                                                                    zero_scale, T, W, H, (uint8_t*)out);
+    EPSB_SLOT_SWITCH(W, (global_reduce_kernel<kRef, kS><<<red_grid(T), kRedThreads, 0, st>>>(
+        (const uint8_t*)recv, glob_map, (const uint8_t*)shared, (const uint8_t*)x, zero_scale, T, W, H, (uint8_t*)out)));
   else
     global_reduce_wide_kernel<kRef><<<red_grid(T), kRedThreads, 0, st>>>((const uint8_t*)recv, glob_map,
                                                                          (const uint8_t*)shared, (const uint8_t*)x,
@@ -477,9 +488,9 @@ extern "C" int epsb_reduce_ep1(const void* y, const int32_t* red_map, const int3
   EPSB_REQUIRE(S > 0, EPSB_ERR_INVALID, "num_stages %d", S);
   EPSB_REQUIRE(zero_scale == nullptr || x != nullptr, EPSB_ERR_INVALID, "zero_scale needs the raw input x");
   if (T <= 0) return EPSB_OK;
-  reduce_ep1_kernel<<<red_grid(T), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  EPSB_SLOT_SWITCH(k, (reduce_ep1_kernel<kS><<<red_grid(T), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)y, red_map, glob_map, ret_incl, S, (const uint8_t*)shared, (const uint8_t*)x, zero_scale, T, k, H,
-      (uint8_t*)out);
+      (uint8_t*)out)));
   return check_launch("reduce_ep1");
 }
 
@@ -489,8 +500,8 @@ extern "C" int epsb_fastep_reduce(const void* rows, const void* raw, const void*
   if (rc) return rc;
   EPSB_REQUIRE(k > 0 && k <= kMaxSlots, EPSB_ERR_INVALID, "topk %d exceeds %d", k, kMaxSlots);
   if (T <= 0) return EPSB_OK;
-  fastep_reduce_kernel<<<red_grid(T), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const uint8_t*)rows, (const uint8_t*)raw, (const uint8_t*)shared, w, mapping, T, k, H, (uint8_t*)out);
+  EPSB_SLOT_SWITCH(k, (fastep_reduce_kernel<kS><<<red_grid(T), kRedThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)rows, (const uint8_t*)raw, (const uint8_t*)shared, w, mapping, T, k, H, (uint8_t*)out)));
   return check_launch("fastep_reduce");
 }
 
