@@ -162,7 +162,7 @@ def run_reference(args, cfg, rank):
     print(json.dumps(line), flush=True)
 
 
-def build_layer(cfg, comm, dev, torch):
+def build_layer(cfg, comm, dev, torch, stages=1):
     """Random-init expert weights of the configuration's architecture, generated and block-quantised on the GPU."""
     from eps_b200 import ops, workloads
     from eps_b200.layer import MoELayerFP8
@@ -188,7 +188,7 @@ def build_layer(cfg, comm, dev, torch):
         shared = (q1, s1, q2, s2)
     torch.cuda.synchronize()
     layer = MoELayerFP8(H, I, cfg.num_experts, cfg.top_k, cfg.tokens_per_rank, wgu, wgu_s, wd, wd_s, comm=comm,
-                        shared=shared, num_stages=1)
+                        shared=shared, num_stages=stages)
     return layer
 
 
@@ -201,6 +201,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (diagnostics only)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (diagnostics only)")
+    ap.add_argument("--stages", type=int, default=None, help="EPS stages (default: 1 on one GPU, 2 on several)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -236,7 +237,8 @@ def main():
     if cfg.num_experts % world:
         raise SystemExit(f"{cfg.num_experts} experts do not shard over {world} ranks")
 
-    layer = build_layer(cfg, comm, dev, torch)
+    stages = args.stages if args.stages else (1 if world == 1 else 2)
+    layer = build_layer(cfg, comm, dev, torch, stages)
     T, H, k = cfg.tokens_per_rank, cfg.hidden, cfg.top_k
     x_h = workloads.make_tokens(cfg, rank).pin_memory()
     idx_h, w_h = workloads.make_routing(cfg, rank)
@@ -352,7 +354,7 @@ def main():
             "vs_baseline": None, "dtype": "fp8_e4m3(fp32 accumulate)", "data": "synthetic",
             "config": {"workload": f"cfg{cfg.cfg_id}:{cfg.name}", "tokens_per_gpu": T, "global_tokens": Tg,
                        "hidden": H, "inter": I, "experts": cfg.num_experts, "experts_per_gpu": EL, "top_k": k,
-                       "shared_inter": cfg.shared_inter, "parallelism": f"ep{world}",
+                       "shared_inter": cfg.shared_inter, "parallelism": f"ep{world}", "stages": stages,
                        "l2": "inputs larger than L2 (expert weights per GPU >> 126 MB); no flush",
                        "gemm_rows_per_gpu": D},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world,

@@ -84,9 +84,8 @@ class MoELayerFP8:
         row_w = sched.gemm_row_weights()
         n += 1
         eps_ = EL // S
-        for s in range(S):
-            sched.dispatch(s)
-            sched.gemm_expand(self.A[:D], s)
+
+        def stage_gemms(s):
             ex = excl[s * eps_:(s + 1) * eps_ + 1]
             ev = self.gateup_events if s == 0 else None
             if ev is not None:
@@ -99,11 +98,39 @@ class MoELayerFP8:
             ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.act[:D], self.act_s[:D], self.wd[s * eps_:(s + 1) * eps_],
                                  self.wd_s[s * eps_:(s + 1) * eps_], ex, out=self.Y[:D], row_w=row_w,
                                  status=self.status)
-            if self.W > 1:
+
+        if self.W == 1:
+            for s in range(S):
+                sched.gemm_expand(self.A[:D], s)
+                stage_gemms(s)
+                n += 3
+        else:
+            # Stage pipeline on two streams (the reference leaves this to its caller): all dispatches are queued on
+            # the communication stream up front, each combine as soon as its stage has been reduced, so the exchange
+            # of stage s+1 / s-1 runs under the GEMMs of stage s.
+            main = torch.cuda.current_stream()
+            comm_stream = self._comm_stream()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            disp_done = [torch.cuda.Event() for _ in range(S)]
+            red_done = [torch.cuda.Event() for _ in range(S)]
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ready)
+                for s in range(S):
+                    sched.dispatch(s)
+                    disp_done[s].record(comm_stream)
+            for s in range(S):
+                main.wait_event(disp_done[s])
+                sched.gemm_expand(self.A[:D], s)
+                stage_gemms(s)
                 sched.local_reduce(self.Y[:D], s, pre_weighted=True)
-                sched.combine(s)
-                n += 1
-            n += 3
+                red_done[s].record(main)
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(red_done[s])
+                    sched.combine(s)
+                n += 4
+            all_back = torch.cuda.Event()
+            all_back.record(comm_stream)
         shared_out = None
         if self.shared is not None and T > 0:
             sgu, sgu_s, sd, sd_s = self.shared
@@ -118,12 +145,18 @@ class MoELayerFP8:
         if out is None:
             out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device)
         if self.W > 1:
+            torch.cuda.current_stream().wait_event(all_back)  # the shared expert above ran under the last combine
             sched.epilogue(out, shared=shared_out, ref_arith=False)
         else:
             sched.reduce_single_rank(self.Y[:D], out, shared=shared_out)
         n += 1
         self.kernel_launches = n
         return out
+
+    def _comm_stream(self):
+        if getattr(self, "_cs", None) is None:
+            self._cs = torch.cuda.Stream(device=self.dev)
+        return self._cs
 
     # ------------------------------------------------------------------ host-buffer entry point
 

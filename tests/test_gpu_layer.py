@@ -48,16 +48,21 @@ LAYER_CASES = [
     (256, 2048, 1408 - 1408 % 128, 16, 4, 0, 0, 1),   # config 0 with I rounded to the 128 grid
     (100, 1024, 512, 8, 4, 4, 256, 2),                # identity experts + shared expert, two stages
     (33, 768, 384, 8, 8, 0, 0, 4),
+    (128, 1024, 512, 32, 8, 0, 0, 1, "zipf"),         # config 2 shape family: decode-size batch, Zipf(1.2) skew
+    (512, 1024, 384, 16, 8, 0, 0, 2, "none"),         # config 3 shape family: I = 3 x 128, top-8, no shared expert
+    (200, 1536, 512, 24, 12, 12, 0, 1, "normal"),     # config 4 shape family: top-12 over FFN + identity experts
 ]
 
 
-@pytest.mark.parametrize("T,H,I,E,k,nz,sh,S", LAYER_CASES)
-def test_layer_vs_oracle(cuda, oracle, T, H, I, E, k, nz, sh, S):
+@pytest.mark.parametrize("case", LAYER_CASES)
+def test_layer_vs_oracle(cuda, oracle, case):
     from eps_b200 import workloads
     from eps_b200.layer import MoELayerFP8
 
+    T, H, I, E, k, nz, sh, S = case[:8]
+    bias = case[8] if len(case) > 8 else ("normal" if nz else "none")
     cfg = workloads.CONFIGS[0].scaled(tokens_per_rank=T, hidden=H, inter=I, num_experts=E, top_k=k,
-                                      num_zero_experts=nz, shared_inter=sh, bias="normal" if nz else "none")
+                                      num_zero_experts=nz, shared_inter=sh, bias=bias)
     x = workloads.make_tokens(cfg)
     idx, w = workloads.make_routing(cfg)
     dev_w, ref_w = _weights(cfg, range(E), cuda, oracle)
