@@ -201,7 +201,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (diagnostics only)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (diagnostics only)")
-    ap.add_argument("--stages", type=int, default=None, help="EPS stages (default: 1 on one GPU, 2 on several)")
+    ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1; at 2 GPUs 1/2/4 stages measured 4.30/4.49/4.57 ms)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -237,7 +237,7 @@ def main():
     if cfg.num_experts % world:
         raise SystemExit(f"{cfg.num_experts} experts do not shard over {world} ranks")
 
-    stages = args.stages if args.stages else (1 if world == 1 else 2)
+    stages = args.stages if args.stages else 1
     layer = build_layer(cfg, comm, dev, torch, stages)
     T, H, k = cfg.tokens_per_rank, cfg.hidden, cfg.top_k
     x_h = workloads.make_tokens(cfg, rank).pin_memory()
