@@ -76,5 +76,44 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TORCH_SRC = os.path.join(HERE, "csrc_torch", "executor_ops.cpp")
+TORCH_LIB = os.path.join(HERE, "libexecutor_.so")
+
+
+def build_torch_ops(force: bool = False) -> str:
+    """Builds libexecutor_.so: the TORCH_LIBRARY registration of the executor ops (namespace `executor`, the
+    reference's library name) over libeps_b200.so.  Host-only C++ (g++), linked against the installed torch."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    build()
+    if not force and not _stale(TORCH_LIB, [TORCH_SRC, LIB, os.path.join(HERE, "..", "include", "eps_b200.h")]):
+        return TORCH_LIB
+    inc = ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", TORCH_SRC, "-o", TORCH_LIB,
+           *[f"-I{i}" for i in inc], f"-L{libdir}", "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda", f"-L{HERE}",
+           "-l:libeps_b200.so", f"-Wl,-rpath,{libdir}", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building libexecutor_.so failed:\n{r.stderr[-4000:]}")
+    return TORCH_LIB
+
+
+def load_torch_ops():
+    """torch.ops.load_library(libexecutor_.so) -> torch.ops.executor (reference python/eps/executor/ops.py:9-17)."""
+    import torch
+
+    if not os.path.exists(TORCH_LIB):
+        raise RuntimeError(f"{TORCH_LIB} is missing: run eps_b200.build.build_torch_ops()")
+    torch.ops.load_library(TORCH_LIB)
+    return torch.ops.executor
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch-ops" in sys.argv:
+        print(build_torch_ops(force="--force" in sys.argv))
