@@ -20,9 +20,7 @@
 //     caller's status words, raises a CTA-wide abort flag, and every role leaves
 //     its loop, waits for copies in flight, frees TMEM and returns.
 //   * no TMA multicast is used anywhere.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace epsb {
 
@@ -45,14 +43,8 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 384;              // warpgroup 0: producers; warpgroups 1,2: epilogue
 constexpr int kTmemCols = 512;             // two accumulator buffers of 256 fp32 columns
 constexpr int kMaxExperts = 1024;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// tcgen05 instruction descriptor, kind::f8f6f4: D=f32 (bits 4-5 = 1), A=B=e4m3 (0), both K-major,
-// N>>3 at bits 17-22, M>>4 at bits 24-28.
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-// Shared-memory matrix descriptor, high word: stride-byte-offset 1024 B (8 rows x 128 B) >> 4 = 64,
-// descriptor version 1 (bits 46-47), layout SWIZZLE_128B = 2 (bits 61-63).
-constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+constexpr uint32_t kIdesc = f8_idesc(kBM, kBN);
 
 template <int kMode>
 struct SharedStorage {
@@ -71,132 +63,6 @@ struct SharedStorage {
   float amax_x[2][2][kBM];  // [tile parity][column half][row]
   int32_t tile_prefix[kMaxExperts + 1];  // m-tiles before each expert
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).
-template <class Storage>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Storage* sm, int32_t* status, int code) {
-  uint64_t t0 = 0;
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try(bar, parity)) return true;
-    if (sm->abort_flag) return false;
-    if ((++spins & 0x3ff) == 0) {
-      const uint64_t now = global_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
-        sm->abort_flag = 1;
-        if (status != nullptr) {
-          atomicCAS(status, 0, code);
-          atomicExch(status + 1, (int)blockIdx.x);
-        }
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Asynchronous TMEM load of 32 columns of this warp's 32 lanes; the registers are valid only after
-// tmem_wait() on the same array (which ties them to the wait through read-write operands, so no use
-// can be scheduled above it).
-__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
-// No instruction: makes later uses of r depend on this point of the (volatile) asm sequence, i.e. on the
-// tcgen05.wait::ld issued just before it.
-__device__ __forceinline__ void tmem_tie(uint32_t (&r)[32]) {
-  asm volatile(""
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
-                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
-                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
-                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
-// One row of the staged tile output -> global memory, asynchronously (bulk copy engine).  dst, src 16-byte aligned.
-__device__ __forceinline__ void bulk_store_row(void* dst, const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// The staging rows written by this thread's earlier bulk copies may be overwritten again.
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void st_shared_16(void* p, uint4 v) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(smem_u32(p)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
 
 struct GemmParams {
   const float* a_s;
@@ -346,7 +212,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const uint64_t db = ((uint64_t)kDescHi << 32) | (uint64_t)((((a_addr + kABytes) >> 4) & 0x3fffu) | (1u << 16));
           const uint32_t d = tmem_base + (uint32_t)buf * kBN;
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 32; k4++) umma_f8(d, da + 2 * k4, db + 2 * k4, k4 > 0 ? 1u : 0u);
+          for (int k4 = 0; k4 < kBK / 32; k4++) umma_f8(d, da + 2 * k4, db + 2 * k4, kIdesc, k4 > 0 ? 1u : 0u);
           umma_commit(&sm->empty[s]);       // stage reusable once these MMAs have read it
           umma_commit(&sm->tmem_full[buf]); // accumulator buffer ready for the epilogue
         }

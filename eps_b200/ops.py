@@ -254,8 +254,12 @@ def silu_run(gate_up, result, exclusive_sum=None, num_experts=0):
 # ------------------------------------------------------------------ grouped GEMM
 
 
-def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None):
-    """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes."""
+def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
+                     tile_tokens=0):
+    """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.
+
+    tile_tokens > 0 selects the token-N kernel (weights on the MMA's M, that many tokens per tile on N);
+    it exists for modes PLAIN and DOWN."""
     _check(A, "A", _FP8, 2)
     _check(a_s, "A_scale", torch.float32, 2)
     _check(B, "B", _FP8, 3)
@@ -275,6 +279,10 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
     else:
         C = out if out is not None else torch.empty((max_rows, N), dtype=torch.bfloat16, device=dev)
         c_s = None
+    if tile_tokens:
+        call("epsb_grouped_gemm_fp8_tn", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K,
+             ptr(C), ptr(row_w), ptr(status), int(tile_tokens), stream_ptr())
+        return C
     call("epsb_grouped_gemm_fp8", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K, ptr(C),
          ptr(c_s), ptr(row_w), ptr(status), stream_ptr())
     return (C, c_s) if mode == GEMM_GATEUP else C

@@ -253,6 +253,18 @@ int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void*
                           const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
                           float* c_s, const float* row_w, int32_t* status, void* stream);
 
+/* The same product with the operand roles swapped ("token-N"): 128 weight rows
+ * are the MMA's M and an expert's tokens its N, so an expert of up to
+ * tile_tokens rows streams its weights exactly once, whatever its row count
+ * (the reference's H20 configuration makes the same swap,
+ * src/gemm/aok_grouped_gemm/src/operations/hopper_grouped_gemm.cu:147-170).
+ * Arguments as epsb_grouped_gemm_fp8; modes EPSB_GEMM_PLAIN and EPSB_GEMM_DOWN.
+ * tile_tokens: tokens per tile, a multiple of 16 in [16, 256]; experts with
+ * more rows take several tiles.  a_s and b_s must be 16-byte aligned. */
+int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
+                             const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
+                             const float* row_w, int32_t* status, int tile_tokens, void* stream);
+
 /* Gathers the per-GEMM-row gate weight: row_w[d] = w_recv[gemm_map[d]] for
  * d < excl[EL] (w_recv is [R,k] flat, gemm_map holds row*k+slot). */
 int epsb_gather_row_weights(const float* w_recv, const int32_t* gemm_map, const int32_t* excl, int num_experts,
