@@ -19,6 +19,9 @@
 //   * every wait on an mbarrier is bounded: after ~2 s it records a code in the
 //     caller's status words, raises a CTA-wide abort flag, and every role leaves
 //     its loop, waits for copies in flight, frees TMEM and returns.
+//   * an m-tile with at most 64 valid rows (an expert's remainder past a multiple of 128, or a small expert) is
+//     computed with the operand roles swapped, from the same shared-memory stage: its two 128-row weight blocks
+//     are the M of two MMAs and its 32 or 64 token rows their N, so its drain costs in proportion to the tokens;
 //   * no TMA multicast is used anywhere.
 #include "tc_ptx.cuh"
 
@@ -81,7 +84,14 @@ struct GemmParams {
 
 struct TileCoord {
   int e, row0, rows_left, n;  // expert, first GEMM row of the tile, valid rows from row0, n-tile index
+  int tail;                   // 0: token rows on the MMA's M; 32 or 64: a tail tile of that many token COLUMNS
 };
+
+// An m-tile with at most kTailMax valid rows (an expert's remainder, or a small expert) is computed with the
+// operand roles swapped: the 2 x 128 weight rows of the tile become two M=128 MMAs and the tokens their N
+// (32 or 64 columns), from the very same shared-memory stage.  Draining TMEM then costs in proportion to the
+// tokens, where the normal orientation drains all 128 x 256 accumulators for a handful of valid rows.
+constexpr int kTailMax = 64;
 
 template <class Storage>
 __device__ __forceinline__ TileCoord locate_tile(int t, const GemmParams& p, const Storage* sm) {
@@ -99,12 +109,130 @@ __device__ __forceinline__ TileCoord locate_tile(int t, const GemmParams& p, con
   const int b = __ldg(p.excl + lo), e_ = __ldg(p.excl + lo + 1);
   c.row0 = b + m * kBM;
   c.rows_left = e_ - c.row0;
+  c.tail = c.rows_left <= 32 ? 32 : (c.rows_left <= kTailMax ? 64 : 0);
   return c;
 }
 
+// Epilogue of a tail tile (see kTailMax).  TMEM lanes = the 128 weight rows of a block, columns [0, T) = block 0
+// (gate rows, or the tile's first 128 weight rows), [T, 2T) = block 1 (up rows, or the second 128), T = 2 * kTh.
+// The warp of quadrant `quad` and column half `half` owns weight rows 32*quad + lane and tokens
+// [half*kTh, (half+1)*kTh) of the tile.  Token scales live one per lane and are broadcast with shuffles.
+template <int kMode, int kTh, class Storage>
+__device__ __forceinline__ bool tail_tile(const GemmParams& p, Storage* sm, const TileCoord& c, int KB, uint32_t& it,
+                                          uint32_t& amax_phase, uint32_t lane_addr, int quad, int half, int lane) {
+  constexpr int kT = 2 * kTh;
+  const int NB = (int)(p.N / 128);
+  const int tok0 = half * kTh;                           // first token (tile-relative) of this warp
+  const bool tok_ok = lane < kTh && tok0 + lane < c.rows_left;
+  const int64_t my_row = (int64_t)c.row0 + tok0 + lane;  // the token whose scale this lane carries
+  const float* as_row = p.a_s + (tok_ok ? my_row : (int64_t)c.row0) * KB;
+  int blk0, blk1;
+  if (kMode == EPSB_GEMM_GATEUP) {
+    blk0 = c.n;
+    blk1 = NB / 2 + c.n;
+  } else {
+    blk0 = c.n * 2;
+    blk1 = min(c.n * 2 + 1, NB - 1);
+  }
+  const float* bs0 = p.b_s + ((int64_t)c.e * NB + blk0) * KB;
+  const float* bs1 = p.b_s + ((int64_t)c.e * NB + blk1) * KB;
+  float acc0[kTh], acc1[kTh];
+#pragma unroll
+  for (int i = 0; i < kTh; i++) acc0[i] = acc1[i] = 0.0f;
+  float sa = tok_ok ? __ldg(as_row) : 0.0f, sb0 = __ldg(bs0), sb1 = __ldg(bs1);
+  for (int kb = 0; kb < KB; kb++, it++) {
+    const float s0 = sa * sb0, s1 = sa * sb1;   // this lane's token, both weight blocks
+    if (kb + 1 < KB) {
+      sa = tok_ok ? __ldg(as_row + kb + 1) : 0.0f;
+      sb0 = __ldg(bs0 + kb + 1);
+      sb1 = __ldg(bs1 + kb + 1);
+    }
+    bool good = mbar_wait(&sm->tmem_full[it & 1u], (it >> 1) & 1u, sm, p.status, 33);
+    good = __all_sync(0xffffffffu, good);
+    if (!good) return false;
+    tc_fence_after();
+    const uint32_t tb = lane_addr + (it & 1u) * (uint32_t)kBN + (uint32_t)tok0;
+    uint32_t v0[kTh], v1[kTh];
+    if constexpr (kTh == 16) {
+      tmem_ld16_async(tb, v0);
+      tmem_ld16_async(tb + kT, v1);
+      tmem_wait16(v0);
+      tmem_tie16(v1);
+    } else {
+      tmem_ld32_async(tb, v0);
+      tmem_ld32_async(tb + kT, v1);
+      tmem_wait(v0);
+      tmem_tie(v1);
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->tmem_empty[it & 1u]);
+#pragma unroll
+    for (int i = 0; i < kTh; i++) {
+      acc0[i] = fmaf(__uint_as_float(v0[i]), __shfl_sync(0xffffffffu, s0, i), acc0[i]);
+      acc1[i] = fmaf(__uint_as_float(v1[i]), __shfl_sync(0xffffffffu, s1, i), acc1[i]);
+    }
+  }
+
+  const int wr = quad * 32 + lane;  // weight row inside a 128-row block
+  if (kMode == EPSB_GEMM_GATEUP) {
+    const int64_t I = p.N / 2;
+    // [tile parity][half][quadrant][token]: the same 512 floats the other orientation uses as [parity][half][row]
+    float* ax = &sm->amax_x[0][0][0] + ((amax_phase * 2 + half) * 4) * 32;
+#pragma unroll
+    for (int i = 0; i < kTh; i++) {
+      const float g = acc0[i], u = acc1[i];
+      const float a = (g * __frcp_rn(1.0f + __expf(-g))) * u;
+      acc0[i] = a;
+      // |a| of a finite float orders like its bit pattern; a NaN (only in token columns past the expert's
+      // rows, never stored) may win the maximum there and nowhere else
+      const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a)));
+      if (lane == i) ax[quad * 32 + i] = __uint_as_float(m);
+    }
+    mbar_arrive(&sm->amax_bar);
+    bool good = mbar_wait(&sm->amax_bar, amax_phase, sm, p.status, 43);
+    good = __all_sync(0xffffffffu, good);
+    if (!good) return false;
+    float amax = 0.0f;
+    if (lane < kTh) amax = fmaxf(fmaxf(ax[lane], ax[32 + lane]), fmaxf(ax[64 + lane], ax[96 + lane]));
+    amax_phase ^= 1;
+    const float scale = __fdiv_rn(amax, kFp8Max);
+    const float inv = __frcp_rn(scale);
+    uint8_t* q_out = reinterpret_cast<uint8_t*>(p.C) + ((int64_t)c.row0 + tok0) * I + (int64_t)c.n * 128 + wr;
+#pragma unroll
+    for (int i = 0; i < kTh; i++) {
+      const float inv_i = __shfl_sync(0xffffffffu, inv, i);
+      if (tok0 + i < c.rows_left)
+        q_out[(int64_t)i * I] = (uint8_t)(cvt_e4m3x2(quant_clamp(acc0[i], inv_i), 0.0f) & 0xffu);
+    }
+    if (quad == 0 && tok_ok) p.c_s[my_row * (I / 128) + c.n] = scale;
+  } else {
+    float wgt = 1.0f;
+    if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr && tok_ok) wgt = __ldg(p.row_w + my_row);
+    const int64_t col0 = (int64_t)c.n * kBN + wr;
+    const bool blk1_ok = (int64_t)c.n * kBN + 128 < p.N;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + ((int64_t)c.row0 + tok0) * p.N + col0;
+#pragma unroll
+    for (int i = 0; i < kTh; i++) {
+      const float w = __shfl_sync(0xffffffffu, wgt, i);
+      if (tok0 + i < c.rows_left) {
+        out[(int64_t)i * p.N] = __float2bfloat16_rn(acc0[i] * w);
+        if (blk1_ok) out[(int64_t)i * p.N + 128] = __float2bfloat16_rn(acc1[i] * w);
+      }
+    }
+  }
+  return true;
+}
+
+// Tensor maps of the activation matrix: a box of 128 rows for the normal tiles and boxes of 64 and 32 rows for
+// tail tiles, which then fill 8 or 4 KB of the stage's A region instead of 16.
+struct AMaps {
+  CUtensorMap rows128, rows64, rows32;
+};
+
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   using Storage = SharedStorage<kMode>;
@@ -182,9 +310,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!(ok = mbar_wait(&sm->empty[s], ph ^ 1, sm, p.status, 11))) break;
-          mbar_expect_tx(&sm->full[s], kStageBytes);
+          mbar_expect_tx(&sm->full[s], (c.tail ? c.tail * kBK : kABytes) + kBBytes);
           uint8_t* base = sm->tiles[s];
-          tma_load_2d(base, &tmap_a, kb * kBK, c.row0, &sm->full[s]);
+          tma_load_2d(base, c.tail == 0 ? &tmap_a.rows128 : (c.tail == 64 ? &tmap_a.rows64 : &tmap_a.rows32), kb * kBK,
+                      c.row0, &sm->full[s]);
           tma_load_2d(base + kABytes, &tmap_b, kb * kBK, brow0, &sm->full[s]);
           tma_load_2d(base + kABytes + kABytes, &tmap_b, kb * kBK, brow1, &sm->full[s]);
         }
@@ -199,6 +328,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int tail = locate_tile(t, p, sm).tail;
+        const uint32_t idesc_tail = f8_idesc(128, tail);
         for (int kb = 0; kb < KB; kb++, it++) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -211,8 +342,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const uint64_t da = ((uint64_t)kDescHi << 32) | (uint64_t)(((a_addr >> 4) & 0x3fffu) | (1u << 16));
           const uint64_t db = ((uint64_t)kDescHi << 32) | (uint64_t)((((a_addr + kABytes) >> 4) & 0x3fffu) | (1u << 16));
           const uint32_t d = tmem_base + (uint32_t)buf * kBN;
+          if (tail == 0) {
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 32; k4++) umma_f8(d, da + 2 * k4, db + 2 * k4, kIdesc, k4 > 0 ? 1u : 0u);
+            for (int k4 = 0; k4 < kBK / 32; k4++) umma_f8(d, da + 2 * k4, db + 2 * k4, kIdesc, k4 > 0 ? 1u : 0u);
+          } else {
+            // weights on M (two 128-row blocks of the stage's B region), the tile's token rows on N
+            const uint64_t dw1 =
+                ((uint64_t)kDescHi << 32) | (uint64_t)((((a_addr + 2 * kABytes) >> 4) & 0x3fffu) | (1u << 16));
+#pragma unroll
+            for (int k4 = 0; k4 < kBK / 32; k4++) {
+              umma_f8(d, db + 2 * k4, da + 2 * k4, idesc_tail, k4 > 0 ? 1u : 0u);
+              umma_f8(d + (uint32_t)tail, dw1 + 2 * k4, da + 2 * k4, idesc_tail, k4 > 0 ? 1u : 0u);
+            }
+          }
           umma_commit(&sm->empty[s]);       // stage reusable once these MMAs have read it
           umma_commit(&sm->tmem_full[buf]); // accumulator buffer ready for the epilogue
         }
@@ -232,6 +374,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord c = locate_tile(t, p, sm);
+      if (c.tail != 0) {
+        ok = c.tail == 32 ? tail_tile<kMode, 16>(p, sm, c, KB, it, amax_phase, lane_addr, quad, half, lane)
+                          : tail_tile<kMode, 32>(p, sm, c, KB, it, amax_phase, lane_addr, quad, half, lane);
+        continue;
+      }
       const int64_t grow = (int64_t)c.row0 + r_in_tile;
       const bool row_ok = r_in_tile < c.rows_left;
       const float* as_row = p.a_s + (row_ok ? grow : (int64_t)c.row0) * KBs;
@@ -397,13 +544,13 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// 2-D e4m3 tensor [rows, K] (K contiguous), box 128 x 128, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K) {
+// 2-D e4m3 tensor [rows, K] (K contiguous), box 128 bytes x box_rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows = 128) {
   EncodeFn fn = encode_fn();
   if (fn == nullptr) return fail(EPSB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, 128u};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -413,7 +560,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K) {
 }
 
 template <int kMode>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+int launch(const AMaps& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   const size_t smem = sizeof(SharedStorage<kMode>) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -448,8 +595,13 @@ extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, 
   EPSB_REQUIRE((int64_t)num_experts * N < (1ll << 31) && max_rows < (1ll << 31), EPSB_ERR_INVALID,
                "tensor too large for 32-bit TMA coordinates");
   if (max_rows <= 0) return EPSB_OK;
-  CUtensorMap ta, tb;
-  int rc = make_map(&ta, A, max_rows, K);
+  AMaps ta;
+  CUtensorMap tb;
+  int rc = make_map(&ta.rows128, A, max_rows, K, 128);
+  if (rc) return rc;
+  rc = make_map(&ta.rows64, A, max_rows, K, 64);
+  if (rc) return rc;
+  rc = make_map(&ta.rows32, A, max_rows, K, 32);
   if (rc) return rc;
   rc = make_map(&tb, B, (int64_t)num_experts * N, K);
   if (rc) return rc;

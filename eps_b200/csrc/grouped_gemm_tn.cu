@@ -1,22 +1,26 @@
-// FP8 block-scaled grouped GEMM, "token-N" orientation, for experts with few rows (sm_100a).
+// FP8 block-scaled grouped GEMM, "token-N" orientation (sm_100a).
 //
 // Same arithmetic as grouped_gemm.cu, with the operand roles swapped (what the reference does on H20 with its
 // swap-AB tiles, src/gemm/aok_grouped_gemm/src/operations/hopper_grouped_gemm.cu:147-170): the 128 rows of a WEIGHT
 // tile are the MMA's M (TMEM lanes) and an expert's tokens are its N (TMEM columns, any multiple of 16 up to 256).
-// Why: with tokens on M, an expert of 140 rows costs two 128-row tiles and each tile a full pass over the weights;
-// with tokens on N it is ONE tile of N = 144, the accumulator is 144 columns wide instead of 256, so three (or, for
-// decode-sized experts, eight) K steps fit in TMEM at once and the MMA <-> epilogue hand-off latency that bounds the
-// other kernel is covered.  The kernel is then bound by weight streaming.
+// An expert of up to tile_tokens rows is then ONE tile whatever its row count and streams its weights exactly once;
+// the accumulator is tile_tokens columns wide, so 512 / round32(tile_tokens) K steps fit in TMEM at once.
 //
 // Roles (384 threads, one CTA per SM, persistent over a device-built tile list):
 //   warp 0    TMA producer: weight tile (128 x 128 B) + token rows (boxes of 256/128/64/32/16 rows) per K step
 //   warp 1    MMA issuer (tcgen05.mma kind::f8f6f4, M128, N = tokens of the tile), TMEM allocation
-//   warps 2,3 scale loaders: a_s[token, kb] * b_s[block, kb] for the tile's tokens into a shared-memory ring,
-//             several K steps ahead (the epilogue needs one scale per COLUMN here)
-//   warps 4-11 epilogue: drain TMEM per K step (16 columns at a time), fold into fp32 registers, then transpose the
-//             tile through shared memory and store token rows with asynchronous bulk copies
+//   warps 2,3 scale loaders: a_s[token, kb] * b_s[block, kb] for the tile's tokens into a shared-memory ring, in
+//             batches of four K steps (the epilogue needs one scale per COLUMN in this orientation)
+//   warps 4-11 epilogue: drain TMEM per K step with the 16x256b load shape, fold into fp32 registers, then
+//             transpose the tile through warp-private shared memory and store coalesced 16-byte pieces
 // Every mbarrier wait is bounded (status words as in grouped_gemm.cu); no TMA multicast.
+//
+// Where it stands: the per-K-step synchronisation chain of the epilogue (two waits, TMEM loads, release) costs
+// about as much for 128 weight rows here as for 256 in grouped_gemm.cu, so at 128 rows per expert this kernel
+// runs at about 60 % of the other one's speed and the host side does not select it by default; it is kept as the
+// drop-in for callers that want the reference's swapped orientation and as the base for a leaner K loop.
 #include "tc_ptx.cuh"
+
 
 namespace epsb {
 
@@ -30,7 +34,7 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxBuf = 8;
 constexpr int kScaleBatches = 3;  // batches of four K steps in the scale ring
 constexpr int kMaxExperts = 1024;
-constexpr int kOutRowBytes = 256 + 16;  // one token's 128 bf16 of the tile + padding
+constexpr int kOutRowBytes = 64 + 16;   // one warp's 32 weight rows of one token (bf16) + padding
 constexpr int kSmemLimit = 232448;      // 227 KB
 
 struct TnParams {
@@ -51,7 +55,7 @@ struct TnParams {
   int n_stages;       // TMA ring depth
   int stage_bytes;    // 16 KB + tile_tokens * 128, multiple of 1024
   int ctrl_off, scale_off, out_off;  // byte offsets of the regions behind the tile ring
-  int half_rows;      // token rows one column half can hold in the output staging area
+  int half_rows;      // token columns one epilogue warp can hold in its output staging area
 };
 
 struct Ctrl {
@@ -61,10 +65,9 @@ struct Ctrl {
   uint64_t tmem_empty[kMaxBuf];
   uint64_t sc_full[kScaleBatches];   // one phase per batch of four K steps
   uint64_t sc_empty[kScaleBatches];
-  uint64_t half_bar[2];   // the 128 threads of one column half, around the output staging rows
   uint32_t tmem_base;
   volatile int abort_flag;
-  alignas(16) float row_w[2][128];    // per column half: the gate weights of the tile's tokens (down mode)
+  alignas(16) float row_w[8][128];    // per epilogue warp: the gate weights of its token columns (down mode)
   int32_t tile_prefix[kMaxExperts + 1];  // token tiles before each expert
 };
 
@@ -103,7 +106,7 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_tn) + 1023) & ~(uintptr_t)1023);
   Ctrl* sm = reinterpret_cast<Ctrl*>(base + p.ctrl_off);
   float* sc_ring = reinterpret_cast<float*>(base + p.scale_off);        // [kScaleBatches][4][col_stride]
-  uint8_t* out_stage = base + p.out_off;                                // [2][half_rows tokens][kOutRowBytes]
+  uint8_t* out_stage = base + p.out_off;                                // [8 warps][half_rows tokens][kOutRowBytes]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (int)(p.K / kBK);
 
@@ -120,8 +123,6 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       mbar_init(&sm->sc_full[s], 2);      // one arrival per loader warp
       mbar_init(&sm->sc_empty[s], 8);     // one arrival per epilogue warp
     }
-    mbar_init(&sm->half_bar[0], 128);
-    mbar_init(&sm->half_bar[1], 128);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -156,9 +157,9 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   const int total_tiles = sm->tile_prefix[p.num_experts] * p.w_tiles;
 
   // register budget: see grouped_gemm.cu (128 * dec + 256 * inc <= 384 * 168)
-  static_assert(128 * 56 + 256 * 216 <= kThreads * 168, "setmaxnreg budget exceeds the CTA's register pool");
+  static_assert(128 * 72 + 256 * 208 <= kThreads * 168, "setmaxnreg budget exceeds the CTA's register pool");
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------ TMA producer
       int s = 0;
@@ -317,7 +318,7 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // ------------------------------------------------ epilogue: 8 warps
     // Warp w drains TMEM lanes 32*(w%4).. (weight rows) of one half of the tile's token columns, with the
     // 16x256b load shape: thread t holds rows t/4 + {0, 8, 16, 24} of its quadrant and, per 16-column chunk,
@@ -330,9 +331,10 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     const int half = (warp - 4) >> 2;    // which half of the tile's token columns
     const int tq = lane & 3, tr = lane >> 2;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int tid_half = quad * 32 + lane;   // 0..127 inside the half's warpgroup
-    uint8_t* my_stage = out_stage + (size_t)half * p.half_rows * kOutRowBytes;
-    uint32_t half_phase = 0, tph = 0, sph = 0;
+    const int ew = warp - 4;             // epilogue warp 0..7
+    uint8_t* my_stage = out_stage + (size_t)ew * p.half_rows * kOutRowBytes;   // private to this warp
+    float* my_w = sm->row_w[ew];
+    uint32_t tph = 0, sph = 0;
     int buf = 0, slot = 0;
     bool ok = true;
     auto release_tmem = [&](int b) {
@@ -416,22 +418,21 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
       if (!ok) break;
 
-      // ---- tile epilogue: transpose through shared memory, one token row (128 outputs = 256 B) per bulk copy
+      // ---- tile epilogue, warp-private (no barrier between warps): the warp's 32 weight rows x its token
+      // columns are transposed through its own staging rows (one per token column, 64 bytes of bf16) and leave
+      // as coalesced 16-byte stores.  (Bulk copies are too slow here: the copy engine takes one small copy every
+      // few cycles, and a tile has hundreds of 64-byte pieces.)
       const int col_base = ch0 * 16;               // first token column of this half
-      const int my_cols = my_n * 16;
-      bulk_wait_read();                            // this thread's copies of the previous tile have left the rows
-      if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr)
-        sm->row_w[half][tid_half] = (tid_half < my_cols && col_base + tid_half < tl.valid)
-                                        ? __ldg(p.row_w + tl.row0 + col_base + tid_half)
-                                        : 0.0f;
-      mbar_arrive(&sm->half_bar[half]);
-      ok = mbar_wait(&sm->half_bar[half], half_phase, sm, p.status, 41);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      half_phase ^= 1;
+      const int my_cols = min(my_n * 16, tl.valid - col_base);   // token columns this warp stores (may be <= 0)
+      __syncwarp();                                // every lane has read the previous tile's staging rows
+      if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr) {
+        for (int c = lane; c < my_n * 16; c += 32)
+          my_w[c] = c < my_cols ? __ldg(p.row_w + tl.row0 + col_base + c) : 0.0f;
+        __syncwarp();
+      }
       // Lanes t and t^4 hold adjacent weight rows of the same columns: they swap one value per column pair, so
-      // that each lane stores packed bf16x2 words (two weight rows of one token column).  Staging row = token
-      // column of this half, byte offset = 2 * weight row; a warp's 32 words fall into 32 distinct banks.
+      // that each lane stores packed bf16x2 words (two weight rows of one token column); a warp's 32 words of
+      // one store fall into 32 distinct banks (row pitch 80 bytes).
       {
         const int odd = tr & 1;
 #pragma unroll
@@ -439,8 +440,8 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           if (ch < my_n) {
             float2 wlo = make_float2(1.0f, 1.0f), whi = wlo;
             if (kMode == EPSB_GEMM_DOWN && p.row_w != nullptr) {
-              wlo = *reinterpret_cast<const float2*>(&sm->row_w[half][ch * 16 + 2 * tq]);
-              whi = *reinterpret_cast<const float2*>(&sm->row_w[half][ch * 16 + 2 * tq + 8]);
+              wlo = *reinterpret_cast<const float2*>(my_w + ch * 16 + 2 * tq);
+              whi = *reinterpret_cast<const float2*>(my_w + ch * 16 + 2 * tq + 8);
             }
 #pragma unroll
             for (int hs = 0; hs < 2; hs++) {
@@ -451,27 +452,29 @@ grouped_gemm_fp8_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
                 const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 4);
                 const uint32_t word = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
                 const int col = ch * 16 + 2 * tq + ((r & 4) ? 8 : 0) + odd;
-                const int wrow = quad * 32 + hs * 16 + (tr & ~1) + ((r & 2) ? 8 : 0);
-                *reinterpret_cast<uint32_t*>(my_stage + (size_t)col * kOutRowBytes + wrow * 2) = word;
+                const int lrow = hs * 16 + (tr & ~1) + ((r & 2) ? 8 : 0);   // weight row inside the quadrant
+                *reinterpret_cast<uint32_t*>(my_stage + (size_t)col * kOutRowBytes + lrow * 2) = word;
               }
             }
           }
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&sm->half_bar[half]);
-      ok = mbar_wait(&sm->half_bar[half], half_phase, sm, p.status, 42);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      half_phase ^= 1;
-      if (tid_half < my_cols && col_base + tid_half < tl.valid) {
-        const int64_t row = (int64_t)tl.row0 + col_base + tid_half;
-        bulk_store_row(reinterpret_cast<uint8_t*>(p.C) + (row * p.N + (int64_t)tl.w * kWRows) * 2,
-                       my_stage + (size_t)tid_half * kOutRowBytes, 256);
-        bulk_commit();
+      __syncwarp();
+      // 16-byte pieces back out of the staging rows: four lanes cover one token's 64 bytes, so a warp-wide store
+      // writes eight whole 64-byte segments of C.
+      {
+        uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
+                          (((int64_t)tl.row0 + col_base) * p.N + (int64_t)tl.w * kWRows + quad * 32) * 2 + tq * 16;
+#pragma unroll
+        for (int i = 0; i < kCh * 2; i++) {
+          const int c = i * 8 + tr;
+          if (c < my_cols) {
+            const uint4 v = *reinterpret_cast<const uint4*>(my_stage + (size_t)c * kOutRowBytes + tq * 16);
+            st_16(c_base + (int64_t)c * p.N * 2, v);
+          }
+        }
       }
     }
-    bulk_wait_all();
   }
 
   tc_fence_before();
@@ -533,7 +536,7 @@ int launch_grouped_gemm_tn(int mode, const void* A, const float* a_s, const void
   const int ctrl_bytes = (int)((sizeof(Ctrl) + 127) & ~(size_t)127);
   const int scale_bytes = kScaleBatches * 4 * p.col_stride * 4;
   p.half_rows = ((tile_tokens / 16 + 1) / 2) * 16;
-  const int out_bytes = 2 * p.half_rows * kOutRowBytes;
+  const int out_bytes = 8 * p.half_rows * kOutRowBytes;
   const int fixed = ctrl_bytes + scale_bytes + out_bytes + 1024 + 128;
   p.n_stages = (kSmemLimit - fixed) / p.stage_bytes;
   if (p.n_stages > kMaxStages) p.n_stages = kMaxStages;

@@ -35,6 +35,8 @@ GEMM_CASES = [
     ([130, 0, 7], 256, 512),
     ([64] * 16, 2048, 1408 - 1408 % 128),
     ([300, 5, 0, 129, 128, 1, 77, 256], 512, 2048),
+    # tail tiles (remainders of 1..64 rows run with the operand roles swapped), N % 256 == 128
+    ([129, 160, 33, 64, 65, 32, 193, 31], 384, 256),
 ]
 
 
@@ -54,13 +56,15 @@ def test_gemm_plain(cuda, oracle, rows, N, K):
     got = C.float().cpu().numpy()
     rms = np.sqrt(np.mean(want[:D] ** 2)) if D else 1.0
     # bf16 output rounding (2^-9 relative) + fp32 summation-order differences; tolerance stated vs RMS
-    assert np.max(np.abs(got[:D] - want[:D])) <= 2e-2 * rms
+    # fp32 summation-order differences (vs RMS) plus the bf16 rounding of the output itself (2^-8 relative)
+    assert np.all(np.abs(got[:D] - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
     assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
     assert np.all(got[D:] == 7.0), "rows outside every expert must not be written"
 
 
 @pytest.mark.parametrize("rows,I,K", [([128], 128, 128), ([5, 140], 256, 512), ([64] * 16, 1408 - 1408 % 128, 2048),
-                                       ([200, 0, 3, 131], 2048, 1024)])
+                                       ([200, 0, 3, 131], 2048, 1024),
+                                       ([129, 160, 33, 64, 65, 32, 193, 31, 0, 16], 256, 384)])
 def test_gemm_gateup_swiglu_requant(cuda, oracle, rows, I, K):
     from eps_b200 import ops
 
@@ -85,7 +89,8 @@ def test_gemm_gateup_swiglu_requant(cuda, oracle, rows, I, K):
     assert np.all(np.abs(deq - act[:D]) <= bound)
 
 
-@pytest.mark.parametrize("rows,N,K", [([128], 256, 128), ([9, 250, 0, 40], 512, 1408 - 1408 % 128)])
+@pytest.mark.parametrize("rows,N,K", [([128], 256, 128), ([9, 250, 0, 40], 512, 1408 - 1408 % 128),
+                                       ([130, 64, 33, 1, 161], 384, 256)])
 def test_gemm_down_weighted(cuda, oracle, rows, N, K):
     from eps_b200 import ops
 
@@ -100,7 +105,8 @@ def test_gemm_down_weighted(cuda, oracle, rows, N, K):
     want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl) * row_w[:, None]
     got = C.float().cpu().numpy()
     rms = np.sqrt(np.mean(want[:D] ** 2))
-    assert np.max(np.abs(got[:D] - want[:D])) <= 2e-2 * rms
+    # fp32 summation-order differences (vs RMS) plus the bf16 rounding of the output itself (2^-8 relative)
+    assert np.all(np.abs(got[:D] - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
     assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
 
 
@@ -132,7 +138,8 @@ def test_gemm_token_n_plain(cuda, oracle, rows, N, K, tile):
     want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl)
     got = C.float().cpu().numpy()
     rms = np.sqrt(np.mean(want[:D] ** 2)) if D else 1.0
-    assert np.max(np.abs(got[:D] - want[:D])) <= 2e-2 * rms
+    # fp32 summation-order differences (vs RMS) plus the bf16 rounding of the output itself (2^-8 relative)
+    assert np.all(np.abs(got[:D] - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
     assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
     assert np.all(got[D:] == 7.0), "rows outside every expert must not be written"
 
@@ -155,7 +162,7 @@ def test_gemm_token_n_down_matches_tile_kernel(cuda, oracle, rows, N, K, tile):
     want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl) * row_w[:, None]
     g1, g2 = C1.float().cpu().numpy()[:D], C2.float().cpu().numpy()[:D]
     rms = np.sqrt(np.mean(want[:D] ** 2))
-    assert np.max(np.abs(g2 - want[:D])) <= 2e-2 * rms
+    assert np.all(np.abs(g2 - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
     assert np.max(np.abs(g2 - g1)) <= 2 ** -7 * (np.max(np.abs(want[:D])) + rms)
 
 
