@@ -29,6 +29,9 @@ inline int check_launch(const char* what) {
   return EPSB_OK;
 }
 
+// CTAs a persistent GEMM launch may use: every SM, or the count set with epsb_gemm_set_sm_count().
+int gemm_cta_limit();
+
 inline int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

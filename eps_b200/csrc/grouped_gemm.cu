@@ -621,7 +621,7 @@ extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, 
   // tile-count upper bound without reading the device-side prefix sum
   const int64_t m_tiles_max = (max_rows + kBM - 1) / kBM + num_experts;
   int64_t grid = m_tiles_max * p.n_tiles;
-  if (grid > sm_count()) grid = sm_count();
+  if (grid > gemm_cta_limit()) grid = gemm_cta_limit();
   auto st = static_cast<cudaStream_t>(stream);
   switch (mode) {
     case EPSB_GEMM_GATEUP: return launch<EPSB_GEMM_GATEUP>(ta, tb, p, (int)grid, st);

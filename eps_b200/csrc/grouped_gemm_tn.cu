@@ -557,7 +557,7 @@ int launch_grouped_gemm_tn(int mode, const void* A, const float* a_s, const void
   }
   const int64_t tok_tiles_max = (max_rows + tile_tokens - 1) / tile_tokens + num_experts;
   int64_t grid = tok_tiles_max * p.w_tiles;
-  if (grid > sm_count()) grid = sm_count();
+  if (grid > gemm_cta_limit()) grid = gemm_cta_limit();
   // kCh: 16-column chunks one column half can hold (sets the epilogue's register arrays)
   const int chunks_per_half = (tile_tokens / 16 + 1) / 2;
   const auto st = stream;

@@ -32,6 +32,7 @@ class MoELayerFP8:
         self.S = num_stages
         self.max_tok = max_tokens_per_gpu
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.num_sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
         if hidden % 128 or inter % 128:
             raise EpsError("hidden and intermediate sizes must be multiples of 128")
         if tuple(w_gate_up.shape) != (self.EL, 2 * inter, hidden) or tuple(w_down.shape) != (self.EL, hidden, inter):
@@ -41,7 +42,11 @@ class MoELayerFP8:
         self.sched = Scheduler(top_k, num_experts, hidden, hidden // 128, max_tokens_per_gpu, self.comm, self.EL,
                                input_dtype=torch.uint8, device=self.dev)
         worst = max_tokens_per_gpu * self.W * min(top_k, self.EL)
-        self.max_gemm_rows = min(worst, max_gemm_rows if max_gemm_rows is not None else 2 * max_tokens_per_gpu * top_k)
+        # Like the reference's arenas (src/communication/msccl_comm.cu:191-199) the GEMM-side buffers are sized for
+        # the worst routing by default: every token of every rank lands here with min(k, EL) of its slots.  The
+        # host only learns the number of received TOKENS before it launches the GEMMs (the row count stays on the
+        # device), so a smaller capacity is checked against tokens * min(k, EL), which over-counts by up to k.
+        self.max_gemm_rows = min(worst, max_gemm_rows) if max_gemm_rows is not None else worst
         D = max(self.max_gemm_rows, 1)
         dev = self.dev
         self.A = torch.empty((D, hidden), dtype=torch.uint8, device=dev)
@@ -73,6 +78,20 @@ class MoELayerFP8:
         xq, xs = ops.per_token_group_quant_fp8(x, out=self.xq[:T], out_scales=self.xs[:T])
         n += 1
         Tg = num_global_tokens if num_global_tokens is not None else T * self.W
+        shared_out, shared_done = None, None
+        if self.W == 1 and self.shared is not None and T > 0:
+            # The shared expert needs only the quantised tokens, while the routed path first runs its plan kernels
+            # (single CTAs, ~0.2 ms): run the two side by side.  The GEMMs leave a few SMs to the plan kernels,
+            # which could not start otherwise (a GEMM CTA owns all registers of its SM).
+            main = torch.cuda.current_stream()
+            side = self._comm_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ops.gemm_set_sm_count(max(self.num_sms - 4, 1))
+                shared_out = self._shared_expert(xq, xs, T)
+                ops.gemm_set_sm_count(0)
+                shared_done = torch.cuda.Event()
+                shared_done.record(side)
         excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1)
         n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
         rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)
@@ -131,27 +150,32 @@ class MoELayerFP8:
                 n += 4
             all_back = torch.cuda.Event()
             all_back.record(comm_stream)
-        shared_out = None
-        if self.shared is not None and T > 0:
-            sgu, sgu_s, sd, sd_s = self.shared
-            if T not in self._sh_excl:
-                self._sh_excl[T] = torch.tensor([0, T], dtype=torch.int32, device=self.dev)
-            sh_excl = self._sh_excl[T]
-            ops.grouped_gemm_fp8(ops.GEMM_GATEUP, xq, xs, sgu, sgu_s, sh_excl, out=self.sh_act[:T],
-                                 out_scales=self.sh_act_s[:T], status=self.status)
-            shared_out = ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.sh_act[:T], self.sh_act_s[:T], sd, sd_s,
-                                              sh_excl, out=self.sh_out[:T], status=self.status)
-            n += 2
+        shared_out = self._shared_expert(xq, xs, T) if self.W > 1 else shared_out
         if out is None:
             out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device)
         if self.W > 1:
             torch.cuda.current_stream().wait_event(all_back)  # the shared expert above ran under the last combine
             sched.epilogue(out, shared=shared_out, ref_arith=False)
         else:
+            if shared_done is not None:
+                torch.cuda.current_stream().wait_event(shared_done)
             sched.reduce_single_rank(self.Y[:D], out, shared=shared_out)
-        n += 1
+        n += 1 + (2 if shared_out is not None else 0)
         self.kernel_launches = n
         return out
+
+    def _shared_expert(self, xq, xs, T):
+        """The always-on expert on the quantised tokens; returns its [T, H] bf16 output (None without one)."""
+        if self.shared is None or T == 0:
+            return None
+        sgu, sgu_s, sd, sd_s = self.shared
+        if T not in self._sh_excl:
+            self._sh_excl[T] = torch.tensor([0, T], dtype=torch.int32, device=self.dev)
+        sh_excl = self._sh_excl[T]
+        ops.grouped_gemm_fp8(ops.GEMM_GATEUP, xq, xs, sgu, sgu_s, sh_excl, out=self.sh_act[:T],
+                             out_scales=self.sh_act_s[:T], status=self.status)
+        return ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.sh_act[:T], self.sh_act_s[:T], sd, sd_s, sh_excl,
+                                    out=self.sh_out[:T], status=self.status)
 
     def _comm_stream(self):
         if getattr(self, "_cs", None) is None:

@@ -254,6 +254,11 @@ def silu_run(gate_up, result, exclusive_sum=None, num_experts=0):
 # ------------------------------------------------------------------ grouped GEMM
 
 
+def gemm_set_sm_count(sm_count: int) -> None:
+    """SMs the persistent GEMM kernels may occupy from now on (0 = all); the sm_count of the reference's aok_create."""
+    call("epsb_gemm_set_sm_count", int(sm_count))
+
+
 def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
                      tile_tokens=0):
     """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.

@@ -246,6 +246,13 @@ int epsb_silu_run(const void* gate_up, void* act, const int32_t* exclusive_sum, 
  * mode EPSB_GEMM_DOWN  : C [max_rows, N] bf16 = result * row_w[m] (fp32), the
  *      top-k gate weight of GEMM row m; row_w NULL = 1.
  * -------------------------------------------------------------------------- */
+/* SMs the persistent GEMM kernels may occupy (one CTA each); 0 = all of them.
+ * ref: the sm_count argument of aok_create (src/executor/aok_grouped_gemm.cu:12,34,
+ * src/executor/bindings/aok_grouped_gemm_ops.cu).  Process-wide; set it before
+ * the launches it should apply to (e.g. to leave SMs to a kernel running on
+ * another stream). */
+int epsb_gemm_set_sm_count(int sm_count);
+
 #define EPSB_GEMM_PLAIN 0
 #define EPSB_GEMM_GATEUP 1
 #define EPSB_GEMM_DOWN 2
