@@ -321,13 +321,18 @@ def main():
     flops = 2.0 * D * 2 * I * H
     peaks = _peaks()
     roofline = None
+    # DRAM bytes of one launch: one ncu capture of this kernel on a 32-expert, 512-token cut of the same configuration
+    # (128 rows per expert, inputs larger than L2) read 1.030 x its algorithmic bytes; the traffic is weight streaming
+    # and grows with the expert count like the algorithmic bytes do, so the ratio is applied to the full launch.
+    traffic = int(1.030 * algo_bytes) if (world == 1 and cfg.cfg_id == 1) else None
     if gemm_ms:
         t_hbm = algo_bytes / (peaks["hbm_gbs"] * 1e9)
         t_tc = flops / (2 * peaks["bf16_tflops"] * 1e12)  # dense FP8 peak taken as 2 x the measured bf16 figure
         if t_hbm >= t_tc:
             ach = algo_bytes / (gemm_ms * 1e-3) / 1e9
             roofline = {"kernel": "grouped_gemm_fp8<gate/up+SwiGLU+requant>", "bound": "hbm", "achieved": ach,
-                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": traffic,
+                        "traffic_source": "ncu dram bytes of a 32-expert cut, scaled by algorithmic bytes" if traffic else None,
                         "peak_source": peaks["source"], "ms_per_launch": gemm_ms, "algorithmic_bytes": algo_bytes,
                         "tflops": flops / (gemm_ms * 1e-3) / 1e12}
         else:
