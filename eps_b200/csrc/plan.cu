@@ -2,14 +2,21 @@
 //
 // Every plan of the reference is a stable counting sort whose visiting order is
 // an artefact of a strided single-CTA thread decomposition.  Here each plan is
-// one CTA of 32 warps running the same primitive: the positions are put in the
-// reference's visiting order ("virtual order"), cut into one contiguous range
-// per warp, counted per warp with warp-match votes (no atomics), scanned over
-// warps and over buckets, and emitted by rank.  The outputs are bit-identical
-// to the reference's, including for inputs that repeat an expert id inside a token.
+// a thread-block cluster of 1 to 8 CTAs of 32 warps running the same primitive:
+// the positions are put in the reference's visiting order ("virtual order"), cut
+// into one contiguous range per warp of the cluster, counted per warp with
+// warp-match votes (no atomics), scanned over warps, over the cluster's CTAs
+// (each CTA reads the others' bucket totals through distributed shared memory)
+// and over buckets, and emitted by rank.  The outputs are bit-identical to the
+// reference's, including for inputs that repeat an expert id inside a token.
+#include <cooperative_groups.h>
+
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace epsb {
 
@@ -19,23 +26,46 @@ constexpr int kPlanThreads = 1024;
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kMaxBuckets = 1024;
 
+constexpr int kMaxCluster = 8;  // portable cluster size
+
 struct SortScratch {
-  int32_t* rows;   // [kPlanWarps][B] per-warp counts, then per-warp exclusive offsets
-  int32_t* base;   // [B] exclusive scan of the bucket totals
-  int32_t* total;  // [B]
-  int32_t* wsum;   // [kPlanWarps + 1]
+  int32_t* rows;    // [kPlanWarps][B] per-warp counts, then per-warp exclusive offsets inside this CTA
+  int32_t* base;    // [B] exclusive scan of the bucket totals (whole cluster)
+  int32_t* total;   // [B] bucket totals of the whole cluster
+  int32_t* ltotal;  // [B] bucket totals of this CTA; the other CTAs of the cluster read it
+  int32_t* cbase;   // [B] sum of the totals of the CTAs before this one
+  int32_t* wsum;    // [kPlanWarps + 1]
 };
+
+constexpr int kScratchRows = kPlanWarps + 4;
 
 __device__ __forceinline__ SortScratch carve(int32_t* smem, int B) {
   SortScratch s;
   s.rows = smem;
   s.base = smem + kPlanWarps * B;
   s.total = s.base + B;
-  s.wsum = s.total + B;
+  s.ltotal = s.total + B;
+  s.cbase = s.ltotal + B;
+  s.wsum = s.cbase + B;
   return s;
 }
 
-size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)(kPlanWarps + 2) * B + kPlanWarps + 2); }
+size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)kScratchRows * B + kPlanWarps + 2); }
+
+std::atomic<int> g_max_cluster{kMaxCluster};
+
+// CTAs per plan: one per 1024 items, a power of two up to the portable cluster size (or the caller's limit).
+int cluster_size_for(int64_t n_items) {
+  const int limit = g_max_cluster.load(std::memory_order_relaxed);
+  int c = 1;
+  while (c * 2 <= limit && (int64_t)c * kPlanThreads < n_items) c *= 2;
+  return c;
+}
+// Items one CTA of a c-CTA cluster owns (what its key cache has to hold).
+int64_t cta_items(int64_t n_items, int c) {
+  const int64_t per_warp = ((n_items + (int64_t)c * kPlanThreads - 1) / ((int64_t)c * kPlanThreads)) * 32;
+  return per_warp * kPlanWarps;
+}
 
 // Shared memory left for the key cache (uint16 per item) after the scratch of a B-bucket sort.
 constexpr size_t kPlanSmemBudget = 200 * 1024;
@@ -46,7 +76,7 @@ size_t key_cache_bytes(int B, int64_t n_items) {
 }
 __device__ __forceinline__ uint16_t* cache_after(int32_t* smem, int B, int cache_items) {
   if (cache_items <= 0) return nullptr;
-  return reinterpret_cast<uint16_t*>(smem + (kPlanWarps + 2) * B + kPlanWarps + 2);
+  return reinterpret_cast<uint16_t*>(smem + kScratchRows * B + kPlanWarps + 2);
 }
 
 // Inclusive scan of one value per thread over the whole 1024-thread CTA.
@@ -99,17 +129,21 @@ __device__ __forceinline__ int strided_order(int v, int n, int NT) {
 // hold the exclusive bucket offsets and the bucket sizes.
 template <class P>
 __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16_t* key_cache = nullptr) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned lt_mask = (1u << lane) - 1u;
   // Items (position, slot) are numbered position-major; a warp owns a contiguous range of items and
-  // visits it 32 at a time, so the lane order inside a step is the visiting order.  Keys of kKeyUnroll
-  // steps are fetched together (independent global loads in flight) and, when the caller provides room,
-  // cached in shared memory so that the emission pass does not touch global memory for them again.
+  // visits it 32 at a time, so the lane order inside a step is the visiting order; warps are numbered
+  // through the cluster (CTA-major).  Keys of kKeyUnroll steps are fetched together (independent global
+  // loads in flight) and, when the caller provides room, cached in shared memory (indexed from the CTA's
+  // first item) so that the emission pass does not touch global memory for them again.
   constexpr int kKeyUnroll = 4;
   const int J = p.slots();
   const int n_items = n_pos * J;
-  const int chunk = ((n_items + kPlanThreads - 1) / kPlanThreads) * 32;
-  const int i_begin = min(n_items, warp * chunk), i_end = min(n_items, i_begin + chunk);
+  const int chunk = ((n_items + C * kPlanThreads - 1) / (C * kPlanThreads)) * 32;
+  const int cta_begin = min(n_items, crank * kPlanWarps * chunk);
+  const int i_begin = min(n_items, (crank * kPlanWarps + warp) * chunk), i_end = min(n_items, i_begin + chunk);
   for (int i = threadIdx.x; i < kPlanWarps * B; i += kPlanThreads) s.rows[i] = 0;
   __syncthreads();
   int32_t* my_row = s.rows + warp * B;
@@ -125,7 +159,7 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16
       const int i = i0 + u * 32 + lane;
       if (i0 + u * 32 < i_end) {  // warp-uniform
         const int key = keys[u];
-        if (key_cache != nullptr && i < i_end) key_cache[i] = (uint16_t)key;  // -1 -> 0xffff
+        if (key_cache != nullptr && i < i_end) key_cache[i - cta_begin] = (uint16_t)key;  // -1 -> 0xffff
         const unsigned m = __match_any_sync(0xffffffffu, key);
         if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
         __syncwarp();
@@ -141,7 +175,18 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16
       s.rows[w * B + b] = run;
       run += c;
     }
-    s.total[b] = run;
+    s.ltotal[b] = run;
+  }
+  cluster.sync();  // every CTA's bucket totals are in its shared memory
+  for (int b = threadIdx.x; b < B; b += kPlanThreads) {
+    int before = 0, all = 0;
+    for (int c = 0; c < C; c++) {
+      const int v = c == crank ? s.ltotal[b] : cluster.map_shared_rank(s.ltotal, c)[b];
+      if (c < crank) before += v;
+      all += v;
+    }
+    s.cbase[b] = before;
+    s.total[b] = all;
   }
   __syncthreads();
   {
@@ -156,7 +201,7 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16
     for (int u = 0; u < kKeyUnroll; u++) {
       const int i = i0 + u * 32 + lane;
       if (i >= i_end) keys[u] = -1;
-      else if (key_cache != nullptr) keys[u] = key_cache[i] == 0xffffu ? -1 : (int)key_cache[i];
+      else if (key_cache != nullptr) keys[u] = key_cache[i - cta_begin] == 0xffffu ? -1 : (int)key_cache[i - cta_begin];
       else keys[u] = p.key(i / J, i % J);
     }
 #pragma unroll
@@ -166,7 +211,7 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16
         const int key = keys[u];
         const unsigned m = __match_any_sync(0xffffffffu, key);
         int mine = 0;
-        if (key >= 0) mine = s.base[key] + my_row[key] + __popc(m & lt_mask);
+        if (key >= 0) mine = s.base[key] + s.cbase[key] + my_row[key] + __popc(m & lt_mask);
         __syncwarp();
         if (key >= 0 && (m & lt_mask) == 0) my_row[key] += __popc(m);
         __syncwarp();
@@ -177,12 +222,21 @@ __device__ void stable_bucket_sort(P& p, int n_pos, int B, SortScratch s, uint16
       }
     }
   }
-  __syncthreads();
+  // What the CTAs emitted to global memory is visible to the whole cluster, and nobody reads this CTA's
+  // bucket totals any more, once every CTA is past this point.
+  __threadfence();
+  cluster.sync();
 }
+
+// Thread index and thread count of the whole cluster, for the element-wise loops around the sorts.
+__device__ __forceinline__ int cluster_tid() { return (int)cg::this_cluster().block_rank() * kPlanThreads + threadIdx.x; }
+__device__ __forceinline__ int cluster_threads() { return (int)cg::this_cluster().num_blocks() * kPlanThreads; }
+__device__ __forceinline__ bool cluster_leader() { return cg::this_cluster().block_rank() == 0; }
 
 // Inclusive count at the end of every (group, stage) run of buckets.
 __device__ __forceinline__ void write_stage_sums(const SortScratch& s, int groups, int EL, int S, int32_t* out) {
   const int EPS = EL / S;
+  if (!cluster_leader()) return;
   for (int i = threadIdx.x; i < groups * S; i += kPlanThreads) {
     const int g = i / S, st = i % S;
     const int last = g * EL + (st + 1) * EPS - 1;
@@ -244,7 +298,7 @@ source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w
   SortScratch s = carve(plan_smem, E);
   uint16_t* cache = cache_after(plan_smem, E, cache_items);
   if (zero_scale != nullptr && weights != nullptr) {
-    for (int t = threadIdx.x; t < T; t += kPlanThreads) {
+    for (int t = cluster_tid(); t < T; t += cluster_threads()) {
       float z = 0.0f;
       for (int j = 0; j < k; j++)
         if (idx[(size_t)t * k + j] < 0) z += weights[(size_t)t * k + j];
@@ -258,8 +312,9 @@ source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w
   write_stage_sums(s, W, EL, S, send_incl);
   if (glob_map == nullptr) return;
   const int n_sent = s.base[E - 1] + s.total[E - 1];
-  for (int i = threadIdx.x; i < T * W; i += kPlanThreads) glob_map[i] = T * W;
-  __syncthreads();  // send_map and the glob_map fill are visible to the whole CTA
+  for (int i = cluster_tid(); i < T * W; i += cluster_threads()) glob_map[i] = T * W;
+  __threadfence();
+  cg::this_cluster().sync();  // the glob_map fill (and, from the sort above, send_map) is visible to the cluster
   GlobalPlanProblem gp{idx, send_map, glob_map, T, k, W, EL};
   stable_bucket_sort(gp, n_sent, E, s, cache);
   write_stage_sums(s, W, EL, S, coll_incl);
@@ -350,11 +405,13 @@ expert_plans_kernel(const int32_t* __restrict__ ridx, const int32_t* __restrict_
     SortScratch s = carve(plan_smem, EL);
     GemmPlanProblem gp{ridx, gemm_map, inv_gemm, R, k, lo, hi, NT};
     stable_bucket_sort(gp, R, EL, s, cache);
-    for (int e = threadIdx.x; e < EL; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
-    if (threadIdx.x == 0) excl[0] = 0;
+    if (cluster_leader()) {
+      for (int e = threadIdx.x; e < EL; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
+      if (threadIdx.x == 0) excl[0] = 0;
+    }
   }
   if (scale_map == nullptr) return;
-  __syncthreads();  // inv_gemm is complete and visible
+  __syncthreads();  // inv_gemm is complete and visible (the sort ended with a cluster-wide fence and barrier)
   SortScratch s = carve(plan_smem, W * EL);
   LocalReducePlanProblem lp{ridx, recv_incl, inv_gemm, scale_map, red_map, k, lo, hi, W, S, EL};
   stable_bucket_sort(lp, R, W * EL, s, cache);
@@ -388,6 +445,7 @@ fastep_expand_plan_kernel(const int32_t* __restrict__ idx, int T, int k, int E, 
   SortScratch s = carve(plan_smem, E);
   FastEpExpandProblem fp{idx, mapping, s.base, s.total, k};
   stable_bucket_sort(fp, T, E, s);
+  if (!cluster_leader()) return;
   for (int e = threadIdx.x; e < E; e += kPlanThreads) excl[e + 1] = s.base[e] + s.total[e];
   if (threadIdx.x == 0) excl[0] = 0;
 }
@@ -466,6 +524,26 @@ int static_inv_gemm_scratch(int32_t** out) {
   return EPSB_OK;
 }
 
+// Launch of a plan kernel as one cluster of `c` CTAs.
+template <class... KArgs, class... Args>
+int launch_cluster(void (*kernel)(KArgs...), int c, size_t smem, cudaStream_t st, const char* what, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)c, 1, 1);
+  cfg.blockDim = dim3(kPlanThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return fail(EPSB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return check_launch(what);
+}
+
 int set_smem(const void* fn, size_t bytes) {
   if (bytes > 227 * 1024) return fail(EPSB_ERR_INVALID, "plan needs %zu bytes of shared memory (> 227 KB)", bytes);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -478,6 +556,13 @@ int set_smem(const void* fn, size_t bytes) {
 }  // namespace epsb
 
 using namespace epsb;
+
+extern "C" int epsb_plan_set_max_cluster(int max_ctas) {
+  EPSB_REQUIRE(max_ctas == 1 || max_ctas == 2 || max_ctas == 4 || max_ctas == 8, EPSB_ERR_INVALID,
+               "max_ctas %d is not 1, 2, 4 or 8", max_ctas);
+  g_max_cluster.store(max_ctas, std::memory_order_relaxed);
+  return EPSB_OK;
+}
 
 extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, int E, int W, int S,
                                  int32_t* send_map, int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl,
@@ -495,13 +580,14 @@ extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T
     if (coll_incl) cudaMemsetAsync(coll_incl, 0, sizeof(int32_t) * W * S, st);
     return check_launch("source_plans(T=0)");
   }
-  const size_t cache = key_cache_bytes(E, (int64_t)T * W);
+  const int c = cluster_size_for((int64_t)T * W);
+  const int64_t per_cta = cta_items((int64_t)T * W, c);
+  const size_t cache = key_cache_bytes(E, per_cta);
   const size_t smem = sort_smem_bytes(E) + cache;
   int rc = set_smem((const void*)source_plans_kernel, smem);
   if (rc) return rc;
-  source_plans_kernel<<<1, kPlanThreads, smem, st>>>(idx, weights, T, k, E, W, S, send_map, send_incl, glob_map,
-                                                     coll_incl, zero_scale, cache ? (int)((int64_t)T * W) : 0);
-  return check_launch("source_plans");
+  return launch_cluster(source_plans_kernel, c, smem, st, "source_plans", idx, weights, T, k, E, W, S, send_map,
+                        send_incl, glob_map, coll_incl, zero_scale, cache ? (int)per_cta : 0);
 }
 
 extern "C" int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S, int32_t* recv_incl,
@@ -530,14 +616,15 @@ extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, 
   if (NT > 128) NT = 128;
   if (NT < 1) NT = 1;
   const int Bmax = scale_map ? W * EL : EL;
-  const size_t cache = key_cache_bytes(Bmax, max_rows * k);
+  const int c = cluster_size_for(max_rows * k);
+  const int64_t per_cta = cta_items(max_rows * k, c);
+  const size_t cache = key_cache_bytes(Bmax, per_cta);
   const size_t smem = sort_smem_bytes(Bmax) + cache;
   int rc = set_smem((const void*)expert_plans_kernel, smem);
   if (rc) return rc;
-  expert_plans_kernel<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      ridx, recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl,
-      cache ? (int)(max_rows * k) : 0);
-  return check_launch("expert_plans");
+  return launch_cluster(expert_plans_kernel, c, smem, static_cast<cudaStream_t>(stream), "expert_plans", ridx,
+                        recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl,
+                        cache ? (int)per_cta : 0);
 }
 
 extern "C" int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W,
@@ -562,8 +649,8 @@ extern "C" int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, 
   const size_t smem = sort_smem_bytes(E);
   int rc = set_smem((const void*)fastep_expand_plan_kernel, smem);
   if (rc) return rc;
-  fastep_expand_plan_kernel<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(idx, T, k, E, excl, mapping);
-  return check_launch("fastep_expand_plan");
+  return launch_cluster(fastep_expand_plan_kernel, cluster_size_for((int64_t)T * k), smem,
+                        static_cast<cudaStream_t>(stream), "fastep_expand_plan", idx, T, k, E, excl, mapping);
 }
 
 extern "C" int epsb_fastep_plan(const int32_t* all_gathered, int my_rank, int W, int E, int32_t* remote_recv_plan,

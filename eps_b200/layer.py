@@ -92,6 +92,8 @@ class MoELayerFP8:
                 ops.gemm_set_sm_count(0)
                 shared_done = torch.cuda.Event()
                 shared_done.record(side)
+        # next to the shared expert's GEMMs (which occupy all but four SMs) a plan must fit into single free SMs
+        ops.plan_set_max_cluster(1 if shared_done is not None else 8)
         excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1)
         n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
         rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)

@@ -259,6 +259,11 @@ def gemm_set_sm_count(sm_count: int) -> None:
     call("epsb_gemm_set_sm_count", int(sm_count))
 
 
+def plan_set_max_cluster(max_ctas: int) -> None:
+    """CTAs (1, 2, 4 or 8) the plan kernels may use from now on."""
+    call("epsb_plan_set_max_cluster", int(max_ctas))
+
+
 def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
                      tile_tokens=0):
     """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.

@@ -64,6 +64,12 @@ int epsb_dequant_1x128(const void* q, const float* scales, int64_t rows, int64_t
  * (ref: src/scheduler/gemm_executor_interface.cuh:7-10).  k % 16 == 0. */
 int epsb_quant_block128(const void* w, int64_t n_mats, int64_t n, int64_t k, void* q, float* scales, void* stream);
 
+/* CTAs a plan kernel may use (a thread-block cluster of 1, 2, 4 or 8; default 8, chosen per call from the item
+ * count).  No counterpart in the reference, whose plan kernels are single CTAs.  Process-wide; a caller that
+ * runs a plan next to a kernel occupying almost every SM sets 1, because a cluster only starts once all of its
+ * CTAs fit into one GPC. */
+int epsb_plan_set_max_cluster(int max_ctas);
+
 /* ----------------------------------------------------------------------------
  * EPS scheduler plans.  All emit index layouts bit-identical to the reference.
  * -------------------------------------------------------------------------- */

@@ -79,6 +79,40 @@ def test_eps_plans_bit_exact(cuda, oracle, W, S, E, k, T, nz, max_tok):
         assert ok.sum() == D and np.array_equal(gemm_map.cpu().numpy()[inv[ok]], np.nonzero(ok)[0])
 
 
+def test_plans_same_for_every_cluster_size(cuda):
+    """The plans are launched as clusters of 1..8 CTAs; the index arrays must not depend on the cluster size."""
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(7)
+    E, k, T, W, S = 64, 6, 3000, 2, 2
+    idx, w = random_routing(rng, T, k, E, 3)
+    outs = []
+    try:
+        for c in (1, 2, 4, 8):
+            ops.plan_set_max_cluster(c)
+            src = ops.source_plans(_dev(idx, cuda), _dev(w, cuda), E, W, S)
+            recv_incl = torch.tensor([T // 2, T, T, T], dtype=torch.int32, device=cuda)  # two sources, two stages
+            ridx = _dev(np.where(idx < 0, -1, idx).astype(np.int32), cuda)
+            exp = ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, S, T, T)
+            torch.cuda.synchronize()
+            outs.append([t.cpu().numpy().copy() for t in list(src[:4]) + list(exp)])
+    finally:
+        ops.plan_set_max_cluster(8)
+    n_sent = int(outs[0][1][-1])
+    D = int(outs[0][4][-1])
+    n_red = int(outs[0][9][-1])
+    for o in outs[1:]:
+        assert np.array_equal(o[1], outs[0][1]) and np.array_equal(o[3], outs[0][3])       # send_incl, coll_incl
+        assert np.array_equal(o[0][:n_sent], outs[0][0][:n_sent])                           # send_map
+        assert np.array_equal(o[2][:T * W], outs[0][2][:T * W])                             # glob_map
+        assert np.array_equal(o[4], outs[0][4]) and np.array_equal(o[5][:D], outs[0][5][:D])  # excl, gemm_map
+        assert np.array_equal(o[7][:n_red], outs[0][7][:n_red])
+        assert np.array_equal(o[8][:n_red * k], outs[0][8][:n_red * k])
+        assert np.array_equal(o[9], outs[0][9])
+    with pytest.raises(Exception):
+        ops.plan_set_max_cluster(3)
+
+
 def test_source_plans_empty_tokens(cuda):
     from eps_b200 import ops
 
