@@ -141,10 +141,17 @@ class Scheduler:
                 ctx.n_recv = None
                 rows_bound = T
         else:
-            gathered = self.comm.all_gather(ctx.send_incl)               # [W, W*S] on the device
+            # One all-gather carries both inclusive plans of every rank: what it sends (dispatch) and what it will
+            # collect back (combine).  The rows this rank returns to peer p are the rows p collects from it, so the
+            # host gets the combine windows from the same single read and never waits for the expert plans.
+            both = self.comm.all_gather(torch.cat([ctx.send_incl, ctx.coll_incl]))   # [W, 2*W*S] on the device
+            gathered = both[:, :W * S].contiguous()
             ctx.recv_incl, ctx.remote_offset = ops.recv_plan(gathered, self.rank, W, S)
-            g = gathered.cpu().numpy()                                   # the one host read of the rendezvous
+            g2 = both.cpu().numpy()                                      # the one host read of the rendezvous
+            g = g2[:, :W * S]
             ctx.host_dispatch = dispatch_windows(g, self.rank, W, S)
+            coll = dispatch_windows(g2[:, W * S:], self.rank, W, S)      # (coll_excl, coll_incl, ret_excl, ret_incl)
+            ctx.host_combine = (coll[2], coll[3], coll[0], coll[1])
             ctx.n_recv = int(ctx.host_dispatch[3][-1])
             rows_bound = ctx.n_recv
             if ctx.n_recv > self.arena_rows:
@@ -155,9 +162,6 @@ class Scheduler:
         self._all2all(self.send_idx, self.recv_idx, ctx, -1, combine=False)
         (ctx.excl, ctx.gemm_map, ctx.inv_gemm, ctx.scale_map, ctx.red_map, ctx.ret_incl) = ops.expert_plans(
             self.recv_idx, ctx.recv_incl, k, self.lo, self.hi, W, S, self.max_tok, max(rows_bound, 0))
-        if W > 1:
-            both = torch.stack([ctx.ret_incl, ctx.coll_incl]).cpu().numpy().astype(np.int64)
-            ctx.host_combine = (_excl(both[0]), both[0], _excl(both[1]), both[1])
         return ctx.excl, (ctx.n_recv if ctx.n_recv is not None else rows_bound)
 
     # ------------------------------------------------------------------ data path

@@ -52,6 +52,10 @@ def _worker(rank, world, port, case, q):
         idx, w = workloads.make_routing(cfg, rank, Tr)
         for _ in range(2):  # second call reuses arenas and plans buffers
             out = layer.forward(x.to(dev), idx.to(dev), w.to(dev))
+            ctx = layer.sched.context
+            # the combine windows the host derived from the all-gathered plans == the device's return plan
+            assert np.array_equal(ctx.ret_incl.cpu().numpy(), ctx.host_combine[1]), "return plan mismatch"
+            assert np.array_equal(ctx.coll_incl.cpu().numpy(), ctx.host_combine[3]), "collect plan mismatch"
         torch.cuda.synchronize()
         layer.check_status()
         rq, rs = orc.quant_block128(gu.float().numpy())
