@@ -71,23 +71,29 @@ class Communicator:
         dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1), group=self.group)
         return out
 
-    def exchange(self, sends: list[torch.Tensor | None], recvs: list[torch.Tensor | None]) -> None:
-        """Variable-size all-to-all: sends[p] goes to peer p, recvs[p] is filled by peer p.  Entries are
-        contiguous row slices (possibly empty or None); the slice for this rank itself is copied locally."""
+    def exchange(self, sends, recvs) -> None:
+        """Variable-size all-to-all: sends[p] goes to peer p, recvs[p] is filled by peer p.  An entry is a
+        contiguous row slice (possibly empty or None) or a list of such slices (several arrays exchanged in one
+        grouped call; both sides list them in the same order); the entry for this rank itself is copied locally."""
+        def as_list(x):
+            return [] if x is None else (list(x) if isinstance(x, (list, tuple)) else [x])
+
         me = self.rank
-        if sends[me] is not None and recvs[me] is not None and sends[me].numel():
-            if recvs[me].data_ptr() != sends[me].data_ptr():
-                recvs[me].copy_(sends[me])
+        for snd, rcv in zip(as_list(sends[me]), as_list(recvs[me])):
+            if snd is not None and rcv is not None and snd.numel() and rcv.data_ptr() != snd.data_ptr():
+                rcv.copy_(snd)
         if self.world == 1:
             return
         ops = []
         for step in range(1, self.world):
             dst = (me + step) % self.world
             src = (me - step) % self.world
-            if sends[dst] is not None and sends[dst].numel():
-                ops.append(dist.P2POp(dist.isend, sends[dst], self._global(dst), group=self.group))
-            if recvs[src] is not None and recvs[src].numel():
-                ops.append(dist.P2POp(dist.irecv, recvs[src], self._global(src), group=self.group))
+            for t in as_list(sends[dst]):
+                if t is not None and t.numel():
+                    ops.append(dist.P2POp(dist.isend, t, self._global(dst), group=self.group))
+            for t in as_list(recvs[src]):
+                if t is not None and t.numel():
+                    ops.append(dist.P2POp(dist.irecv, t, self._global(src), group=self.group))
         if ops:
             for w in dist.batch_isend_irecv(ops):
                 w.wait()

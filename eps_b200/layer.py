@@ -100,10 +100,9 @@ class MoELayerFP8:
         if rows_k > self.max_gemm_rows:
             raise EpsError(f"{rows_k} possible GEMM rows exceed max_gemm_rows {self.max_gemm_rows}")
         D = max(rows_k, 1)
-        sched.prologue(expert_weights, xq, xs, self.A_s[:D], raw_input=x)
-        n += 4  # gate weights, hidden rows, scales to send order; scales to GEMM order
-        row_w = sched.gemm_row_weights()
-        n += 1
+        sched.prologue(expert_weights, xq, xs, self.A_s[:D], raw_input=x, defer_exchange=True)
+        n += 5  # gate weights, hidden rows, scales to send order; scales to GEMM order; GEMM-row gate weights
+        row_w = sched.gemm_row_weights() if self.W == 1 else None
         eps_ = EL // S
 
         def stage_gemms(s):
@@ -142,6 +141,9 @@ class MoELayerFP8:
                     disp_done[s].record(comm_stream)
             for s in range(S):
                 main.wait_event(disp_done[s])
+                if s == 0:  # the first dispatch carried the gate weights and the input scales
+                    sched.finish_prologue()
+                    row_w = sched.gemm_row_weights()
                 sched.gemm_expand(self.A[:D], s)
                 stage_gemms(s)
                 sched.local_reduce(self.Y[:D], s, pre_weighted=True)

@@ -176,20 +176,37 @@ class Scheduler:
                         b1=self.W * ctx.num_stages)
 
     def _all2all(self, send: torch.Tensor, recv: torch.Tensor, ctx: Context, stage: int, combine: bool) -> None:
+        self._all2all_many([(send, recv, stage)], ctx, combine)
+
+    def _all2all_many(self, items, ctx: Context, combine: bool) -> None:
+        """One grouped exchange for several (send arena, receive arena, stage) triples."""
         if self.W == 1:
             return  # recv aliases send
         W, S = self.W, ctx.num_stages
-        sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, W, S, stage)
-        self.comm.exchange([send[a:b] for (a, b), _ in sl], [recv[c:d] for _, (c, d) in sl])
+        sends = [[] for _ in range(W)]
+        recvs = [[] for _ in range(W)]
+        for send, recv, stage in items:
+            sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, W, S, stage)
+            for p, ((a, b), (c, d)) in enumerate(sl):
+                sends[p].append(send[a:b])
+                recvs[p].append(recv[c:d])
+        self.comm.exchange(sends, recvs)
 
     def prologue(self, expert_scales: torch.Tensor, hidden_states: torch.Tensor, input_scales=None,
-                 recv_input_scales=None, raw_input: torch.Tensor | None = None) -> None:
+                 recv_input_scales=None, raw_input: torch.Tensor | None = None, defer_exchange: bool = False) -> None:
         """raw_input: the bf16 tokens the identity (zero-computation) experts pass through; defaults to
-        hidden_states when that is bf16 (reference ZeroReducePlan::setRawInput, scheduler.cu:76)."""
+        hidden_states when that is bf16 (reference ZeroReducePlan::setRawInput, scheduler.cu:76).
+        defer_exchange=True (world > 1): the gate weights and the input scales are not exchanged here but ride in
+        the same grouped exchange as the first `dispatch`; `finish_prologue()` must follow that dispatch."""
         ctx = self.context
         ctx.raw_input = raw_input if raw_input is not None else hidden_states
+        defer = defer_exchange and self.W > 1
+        ctx.deferred = [] if defer else None
         self._expand_for_comm(expert_scales, self.send_w, ctx)
-        self._all2all(self.send_w, self.recv_w, ctx, -1, combine=False)
+        if defer:
+            ctx.deferred.append((self.send_w, self.recv_w, -1))
+        else:
+            self._all2all(self.send_w, self.recv_w, ctx, -1, combine=False)
         h = hidden_states.view(torch.uint8) if hidden_states.dtype == torch.float8_e4m3fn else hidden_states
         if h.dtype != self.send_hidden.dtype:
             raise EpsError(f"hidden_states must have dtype {self.send_hidden.dtype}, got {h.dtype}")
@@ -198,12 +215,30 @@ class Scheduler:
             if input_scales is None or recv_input_scales is None or self.send_scales is None:
                 raise EpsError("input_quanted needs input_scales, recv_input_scales and input_scales_dim > 0")
             self._expand_for_comm(input_scales, self.send_scales, ctx)
+            if defer:
+                ctx.deferred.append((self.send_scales, self.recv_scales, -1))
+                ctx.deferred_scales_out = recv_input_scales
+                return
             self._all2all(self.send_scales, self.recv_scales, ctx, -1, combine=False)
             ops.gather_rows(self.recv_scales, recv_input_scales, ctx.gemm_map, self.top_k, ops.INT32_MAX,
                             bounds=ctx.excl, b0=0, b1=self.local_num_experts)
 
+    def finish_prologue(self) -> None:
+        """After the dispatch that carried a deferred prologue: the received input scales go to GEMM order."""
+        ctx = self.context
+        out = getattr(ctx, "deferred_scales_out", None)
+        if out is not None:
+            ops.gather_rows(self.recv_scales, out, ctx.gemm_map, self.top_k, ops.INT32_MAX, bounds=ctx.excl, b0=0,
+                            b1=self.local_num_experts)
+            ctx.deferred_scales_out = None
+
     def dispatch(self, stage_idx: int) -> None:
-        self._all2all(self.send_hidden, self.recv_hidden, self.context, stage_idx, combine=False)
+        ctx = self.context
+        items = [(self.send_hidden, self.recv_hidden, stage_idx)]
+        if getattr(ctx, "deferred", None):
+            items = ctx.deferred + items      # gate weights and input scales of ALL stages go with the first dispatch
+            ctx.deferred = None
+        self._all2all_many(items, ctx, combine=False)
 
     def gemm_expand(self, gemm_input: torch.Tensor, stage_idx: int) -> None:
         """gemm_input[p] = received row gemm_map[p] / top_k for the stage's experts (reference expandForGemm)."""
