@@ -52,10 +52,22 @@ def _worker(rank, world, port, S, E, k, T, q):
             comm.exchange([payload[a:b] for (a, b), _ in sl], [got[c:d] for _, (c, d) in sl])
         want = me["src_of"][:, 1] + 100000 * me["src_of"][:, 0]
         assert np.array_equal(got.numpy().reshape(-1), want)
+        # 2b. two arrays in ONE grouped exchange (what the first dispatch of the layer does)
+        recv_idx2 = torch.full((me["R"], k), -9, dtype=torch.int32)
+        got2 = torch.full((me["R"], 1), -1, dtype=torch.int64)
+        sl = stage_slices(win, world, S, -1)
+        comm.exchange([[send_idx[a:b], payload[a:b]] for (a, b), _ in sl],
+                      [[recv_idx2[c:d], got2[c:d]] for _, (c, d) in sl])
+        assert np.array_equal(recv_idx2.numpy(), me["ridx"]) and np.array_equal(got2.numpy().reshape(-1), want)
         # 3. combine direction: windows from the return plan (sender side) and the collect plan (receiver side)
         ret, coll = me["ret_incl"].astype(np.int64), me["coll_incl"].astype(np.int64)
         ex = lambda a: np.concatenate([[0], a[:-1]])
         cwin = (ex(ret), ret, ex(coll), coll)
+        # ... which the host can derive from the all-gathered collect plans alone: the rows this rank returns to
+        # peer p are the rows p collects from it (Scheduler.rendezvous_and_plan relies on this)
+        gcoll = comm.all_gather(torch.from_numpy(me["coll_incl"]))
+        cw = dispatch_windows(gcoll.numpy(), rank, world, S)
+        assert np.array_equal(cw[3], ret) and np.array_equal(cw[1], coll)
         back = torch.arange(me["R"], dtype=torch.int64).reshape(-1, 1) + 1000000 * rank
         collected = torch.full((int(coll[-1]), 1), -1, dtype=torch.int64)
         for st in range(S):
