@@ -136,6 +136,16 @@ def cpu_sample_experts(cfg):
     return max(1, cfg.num_experts // 4)
 
 
+def config_dict(cfg, world, stages, gemm_rows):
+    """The workload description both arms print (same keys, same values for the same command line)."""
+    return {"workload": f"cfg{cfg.cfg_id}:{cfg.name}", "tokens_per_gpu": cfg.tokens_per_rank,
+            "global_tokens": cfg.tokens_per_rank * world, "hidden": cfg.hidden, "inter": cfg.inter,
+            "experts": cfg.num_experts, "experts_per_gpu": cfg.num_experts // world, "top_k": cfg.top_k,
+            "shared_inter": cfg.shared_inter, "parallelism": f"ep{world}", "stages": stages,
+            "l2": "inputs larger than L2 (expert weights per GPU >> 126 MB); no flush",
+            "gemm_rows_per_gpu": gemm_rows}
+
+
 def run_reference(args, cfg, rank):
     """The CPU arm: the oracle (CPU restatement of the reference's layer semantics), all host threads."""
     if rank != 0:
@@ -153,8 +163,8 @@ def run_reference(args, cfg, rank):
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": cfg.tokens_per_rank / v * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3(fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"cfg{cfg.cfg_id}:{cfg.name}", "tokens_per_gpu": cfg.tokens_per_rank,
-                   "hidden": cfg.hidden, "inter": cfg.inter, "experts": cfg.num_experts, "top_k": cfg.top_k},
+        "config": config_dict(cfg, max(args.gpus, 1), args.stages if args.stages else 1,
+                              cfg.tokens_per_rank * cfg.top_k),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -343,6 +353,8 @@ def main():
                         "peak_source": peaks["source"] + " (2 x bf16)", "ms_per_launch": gemm_ms,
                         "algorithmic_bytes": algo_bytes, "gbs": algo_bytes / (gemm_ms * 1e-3) / 1e9}
 
+    if roofline is not None:
+        roofline["gemm_rows"] = D
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
@@ -357,11 +369,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3(fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"cfg{cfg.cfg_id}:{cfg.name}", "tokens_per_gpu": T, "global_tokens": Tg,
-                       "hidden": H, "inter": I, "experts": cfg.num_experts, "experts_per_gpu": EL, "top_k": k,
-                       "shared_inter": cfg.shared_inter, "parallelism": f"ep{world}", "stages": stages,
-                       "l2": "inputs larger than L2 (expert weights per GPU >> 126 MB); no flush",
-                       "gemm_rows_per_gpu": D},
+            "config": config_dict(cfg, world, stages, T * k),   # nominal rows; rank 0's actual count is in roofline
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": out_h.numel() * 2 * world, "ms_per_step": ms_e2e_total / args.steps},
             "gpu_launches": layer.kernel_launches * args.steps,
