@@ -23,6 +23,8 @@
 //     computed with the operand roles swapped, from the same shared-memory stage: its two 128-row weight blocks
 //     are the M of two MMAs and its 32 or 64 token rows their N, so its drain costs in proportion to the tokens;
 //   * no TMA multicast is used anywhere.
+#include <atomic>
+
 #include "tc_ptx.cuh"
 
 namespace epsb {
@@ -562,12 +564,15 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int bo
 template <int kMode>
 int launch(const AMaps& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   const size_t smem = sizeof(SharedStorage<kMode>) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (kernel, device) pair: set it once per device
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_fp8_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return fail(EPSB_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   grouped_gemm_fp8_kernel<kMode><<<grid, kThreads, smem, st>>>(ta, tb, p);
   return check_launch("grouped_gemm_fp8");

@@ -182,6 +182,28 @@ def test_gemm_token_n_errors(cuda):
         ops.grouped_gemm_fp8(ops.GEMM_GATEUP, A, a_s, B.expand(1, 128, 128).reshape(1, 128, 128), b_s, excl, tile_tokens=16)
 
 
+def test_gemm_sm_count_limit(cuda, oracle):
+    """epsb_gemm_set_sm_count (the sm_count of the reference's aok_create) changes the grid, not the result."""
+    from eps_b200 import ops
+    from eps_b200._lib import EpsError
+
+    rng = np.random.default_rng(5)
+    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, [200, 17, 0, 129], 512, 256)
+    args = (_dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda), _dev(excl, cuda))
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    full = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status)
+    try:
+        ops.gemm_set_sm_count(3)
+        few = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status)
+    finally:
+        ops.gemm_set_sm_count(0)
+    torch.cuda.synchronize()
+    _check_status(status)
+    assert torch.equal(full[:D], few[:D])
+    with pytest.raises(EpsError):
+        ops.gemm_set_sm_count(-1)
+
+
 def test_gemm_errors(cuda):
     from eps_b200 import ops
     from eps_b200._lib import EpsError
