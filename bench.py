@@ -211,7 +211,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (diagnostics only)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (diagnostics only)")
-    ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1; at 2 GPUs 1/2/4 stages measured 4.30/4.49/4.57 ms)")
+    ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1; 1/2 stages measured 3.82/4.09 ms at 2 GPUs and 1/2/4 stages 4.59/5.54/6.03 ms at 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
