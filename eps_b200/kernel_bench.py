@@ -2,7 +2,8 @@
 
   python -m eps_b200.kernel_bench [--rows 32768] [--hidden 7168] [--iters 20]
 
-Prints one JSON line per kernel with the algorithmic bytes, the CUDA-event time and GB/s.  Inputs are larger than
+Prints one JSON line per kernel with the algorithmic bytes, the CUDA-event time and GB/s, then the plan kernels'
+times at cluster sizes 1 and 8.  Inputs are larger than
 L2 (126 MB) at the default sizes.  This is the command the ncu summaries of these kernels were taken from.
 """
 from __future__ import annotations
@@ -34,6 +35,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--experts", type=int, default=256)
     a = ap.parse_args()
     dev = torch.device("cuda")
     R, H, k = a.rows, a.hidden, a.topk
@@ -84,6 +86,25 @@ def main():
 
     for name, nbytes, ms in out:
         print(json.dumps({"kernel": name, "algorithmic_bytes": nbytes, "ms": ms, "GB_per_s": nbytes / ms / 1e6}))
+
+    # plan kernels (latency-bound): one rank's routing of T tokens over `--experts` experts, and the expert-side
+    # plans of the W * T tokens a rank of an EP group of W receives, at cluster sizes 1 and 8
+    E = a.experts
+    g = torch.Generator(device="cpu").manual_seed(1)
+    for W, Tt in ((1, T), (8, T)):
+        idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(Tt)]).to(torch.int32).to(dev)
+        wts = torch.rand((Tt, k), device=dev)
+        R = Tt * W if W == 1 else int(Tt * W * 0.66)          # tokens received: all of them, or ~2/3 at W = 8
+        ridx = torch.randint(0, E, (R, k), dtype=torch.int32, device=dev)
+        recv_incl = torch.tensor([R * (i + 1) // W for i in range(W)], dtype=torch.int32, device=dev)
+        for c in (1, 8):
+            ops.plan_set_max_cluster(c)
+            ms_s = _time(lambda: ops.source_plans(idx, wts, E, W, 1), a.iters)
+            ms_e = _time(lambda: ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, 1, Tt, R), a.iters)
+            print(json.dumps({"kernel": "plans", "tokens": Tt, "experts": E, "top_k": k, "ep_world": W,
+                              "received_tokens": R, "max_cluster": c, "source_plans_us": round(ms_s * 1e3, 1),
+                              "expert_plans_us": round(ms_e * 1e3, 1)}))
+    ops.plan_set_max_cluster(8)
 
 
 if __name__ == "__main__":
