@@ -1,4 +1,4 @@
-// torch op registration of the executor operators over the eps_b200 C ABI.
+// torch op registration of the executor operators (and the router of the utils library) over the eps_b200 C ABI.
 //
 // Mirrors the reference's src/executor/bindings/{bindings.cpp,aok_grouped_gemm_ops.cu,silu_ops.cu}: the same
 // namespace (`executor`), op names and argument lists, registered with TORCH_LIBRARY and loadable with
@@ -90,7 +90,28 @@ void per_token_group_quant_fp8(const at::Tensor& x, at::Tensor& q, at::Tensor& s
                             at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// utils.topk_sigmoid with the reference's argument list (src/utils/bindings/th_topk_sigmoid.cu:13-62): bf16 scores,
+// fp32 bias and scales, int32 indices.  int64 indices (which the reference also takes) are not part of this build.
+void topk_sigmoid_op(at::Tensor scores, at::Tensor bias, at::Tensor expert_scales, at::Tensor expert_indices,
+                     int64_t num_tokens, int64_t num_experts, int64_t num_expert_groups, int64_t topk_groups,
+                     int64_t topk, double route_scale) {
+  check(scores, 2, "scores");
+  check(bias, 1, "bias");
+  check(expert_scales, 2, "expert_scales");
+  check(expert_indices, 2, "expert_indices");
+  TORCH_CHECK(scores.scalar_type() == at::kBFloat16, "scores must be bfloat16");
+  TORCH_CHECK(bias.scalar_type() == at::kFloat, "bias must be float32");
+  TORCH_CHECK(expert_scales.scalar_type() == at::kFloat, "expert_scales must be float32");
+  if (expert_indices.scalar_type() != at::kInt) throw std::runtime_error("Not supported expert_indices data type.");
+  raise_if(epsb_router_topk_sigmoid(scores.data_ptr(), 1, bias.data_ptr<float>(), (int)num_tokens, (int)num_experts,
+                                    (int)num_expert_groups, (int)topk_groups, (int)topk, (float)route_scale,
+                                    (int)num_experts, expert_indices.data_ptr<int32_t>(),
+                                    expert_scales.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()));
+}
+
 }  // namespace
+
+TORCH_LIBRARY(utils, m) { m.def("topk_sigmoid", &topk_sigmoid_op); }
 
 TORCH_LIBRARY(executor, m) {
   m.def("aok_create", &aok_create);

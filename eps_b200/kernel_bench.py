@@ -87,6 +87,13 @@ def main():
     for name, nbytes, ms in out:
         print(json.dumps({"kernel": name, "algorithmic_bytes": nbytes, "ms": ms, "GB_per_s": nbytes / ms / 1e6}))
 
+    # router: T tokens x `--experts` logits, 8 groups of which 4 stay, top-k
+    logits = torch.randn((T, a.experts), device=dev, dtype=torch.bfloat16)
+    rbias = torch.randn(a.experts, device=dev) * 0.1
+    ms = _time(lambda: ops.topk_sigmoid(logits, rbias, 8, 4, k, 2.5), a.iters)
+    print(json.dumps({"kernel": "router topk_sigmoid", "tokens": T, "experts": a.experts, "top_k": k,
+                      "algorithmic_bytes": T * (a.experts * 2 + k * 8), "us": round(ms * 1e3, 1)}))
+
     # plan kernels (latency-bound): one rank's routing of T tokens over `--experts` experts, and the expert-side
     # plans of the W * T tokens a rank of an EP group of W receives, at cluster sizes 1 and 8
     E = a.experts

@@ -259,6 +259,29 @@ def gemm_set_sm_count(sm_count: int) -> None:
     call("epsb_gemm_set_sm_count", int(sm_count))
 
 
+def topk_sigmoid(scores, bias, num_expert_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None,
+                 expert_indices=None, expert_scales=None):
+    """Router (reference utils/topk_sigmoid): scores [T, E] fp32 or bf16 logits, bias [E] fp32 or None ->
+    (expert_indices [T, topk] int32, expert_scales [T, topk] fp32) in the layout the Scheduler reads."""
+    if scores.dtype not in (torch.float32, torch.bfloat16):
+        raise EpsError(f"scores must be float32 or bfloat16, got {scores.dtype}")
+    _check(scores, "scores", scores.dtype, 2)
+    T, E = scores.shape
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != E:
+            raise EpsError(f"bias must have {E} entries")
+    dev = scores.device
+    if expert_indices is None:
+        expert_indices = torch.empty((T, topk), dtype=torch.int32, device=dev)
+    if expert_scales is None:
+        expert_scales = torch.empty((T, topk), dtype=torch.float32, device=dev)
+    call("epsb_router_topk_sigmoid", ptr(scores), int(scores.dtype == torch.bfloat16), ptr(bias), T, E,
+         int(num_expert_groups), int(topk_groups), int(topk), float(route_scale),
+         int(E if num_ffn_experts is None else num_ffn_experts), ptr(expert_indices), ptr(expert_scales), stream_ptr())
+    return expert_indices, expert_scales
+
+
 def plan_set_max_cluster(max_ctas: int) -> None:
     """CTAs (1, 2, 4 or 8) the plan kernels may use from now on."""
     call("epsb_plan_set_max_cluster", int(max_ctas))

@@ -64,6 +64,29 @@ int epsb_dequant_1x128(const void* q, const float* scales, int64_t rows, int64_t
  * (ref: src/scheduler/gemm_executor_interface.cuh:7-10).  k % 16 == 0. */
 int epsb_quant_block128(const void* w, int64_t n_mats, int64_t n, int64_t k, void* q, float* scales, void* stream);
 
+/* ----------------------------------------------------------------------------
+ * Router: group-limited top-k over sigmoid scores; produces the expert_indices /
+ * expert_scales the plans read.
+ * ref: topk_sigmoid (src/utils/topk_sigmoid.cu:158-286, params
+ *      src/utils/topk_sigmoid.cuh:6-19), which the reference instantiates for
+ *      num_experts 256 / 8 groups / topk 8 only and otherwise throws
+ *      "Not supported num_experts: ...".
+ * Here: num_experts a multiple of 32 up to 1024, num_expert_groups dividing it
+ * (<= 32), topk <= 32.
+ *   score = 1/(1+expf(-logit)); biased = score + bias[e] (bias may be NULL);
+ *   group score = sum of the group's two largest biased scores; the topk_groups
+ *   best groups stay; topk times the largest biased score among their experts;
+ *   expert_scales = score * route_scale / (sum of the chosen scores), fp32.
+ * Ties go to the lower id.  Outputs [num_tokens, topk] in selection order.
+ * Ids >= num_ffn_experts are written as -1 - (id - num_ffn_experts), the
+ * identity-expert convention of the scheduler (comm_expander_ver2.cu:70-71);
+ * pass num_ffn_experts = num_experts for no mapping.
+ * logits [num_tokens, num_experts] fp32, or bf16 when logits_are_bf16 != 0.
+ * -------------------------------------------------------------------------- */
+int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16, const float* bias, int num_tokens,
+                             int num_experts, int num_expert_groups, int topk_groups, int topk, float route_scale,
+                             int num_ffn_experts, int32_t* expert_indices, float* expert_scales, void* stream);
+
 /* CTAs a plan kernel may use (a thread-block cluster of 1, 2, 4 or 8; default 8, chosen per call from the item
  * count).  No counterpart in the reference, whose plan kernels are single CTAs.  Process-wide; a caller that
  * runs a plan next to a kernel occupying almost every SM sets 1, because a cluster only starts once all of its

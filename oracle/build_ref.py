@@ -27,6 +27,7 @@ REF_SOURCES = [
     "src/executor/activations.cu",
     "src/quant/fp8.cu",
     "src/common/debug.cu",
+    "src/utils/topk_sigmoid.cu",
 ]
 
 

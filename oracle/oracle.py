@@ -192,6 +192,46 @@ def zero_plan(idx, w):
     return z[:T]
 
 
+def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None):
+    """Router, restating reference src/utils/topk_sigmoid.cu:158-262 in fp32 numpy (vectorised over tokens).
+
+    score = 1/(1+exp(-x)) (:181-184 `sigmoid`, fp32), biased = score + bias (:211-216); group score = sum of the
+    group's two largest biased scores (:65-102); the topk_groups best groups stay (:104-118); topk times the largest
+    biased score among their experts (:120-156); scales = score * (route_scale / sum of chosen scores) (:236-244).
+    Ties go to the lower id, as the reference's strict `>` does.  numpy's exp may differ from the device's expf in
+    the last place, so callers compare the scales with a tolerance and treat index differences at equal scores as ties.
+    -> (indices int32 [T, topk] with ids >= num_ffn_experts mapped to -1-(id-num_ffn), scales fp32 [T, topk],
+        biased scores fp32 [T, E] for the callers' tie check)."""
+    x = np.asarray(scores, dtype=np.float32)
+    T, E = x.shape
+    one = np.float32(1.0)
+    orig = (one / (one + np.exp(-x, dtype=np.float32))).astype(np.float32)
+    biased = orig if bias is None else (orig + np.asarray(bias, dtype=np.float32)[None, :]).astype(np.float32)
+    gsize = E // n_groups
+    neg = np.float32(-np.finfo(np.float32).max)
+    grp = biased.reshape(T, n_groups, gsize)
+    # two largest of each group, ties to the lower index (stable argsort on the negated score)
+    order = np.argsort(-grp, axis=2, kind="stable")
+    first = np.take_along_axis(grp, order[:, :, :1], 2)[:, :, 0]
+    second = np.take_along_axis(grp, order[:, :, 1:2], 2)[:, :, 0] if gsize > 1 else np.full((T, n_groups), neg)
+    gscore = (first + second).astype(np.float32)
+    gorder = np.argsort(-gscore, axis=1, kind="stable")[:, :topk_groups]
+    gmask = np.zeros((T, n_groups), dtype=bool)
+    np.put_along_axis(gmask, gorder, True, 1)
+    cand = np.where(np.repeat(gmask, gsize, axis=1), biased, neg)
+    sel = np.argsort(-cand, axis=1, kind="stable")[:, :topk]
+    chosen = np.take_along_axis(orig, sel, 1)
+    total = np.zeros(T, dtype=np.float32)
+    for j in range(topk):                      # the reference sums in selection order
+        total = (total + chosen[:, j]).astype(np.float32)
+    rescale = (np.float32(route_scale) / total).astype(np.float32)
+    scales = (chosen * rescale[:, None]).astype(np.float32)
+    idx = sel.astype(np.int32)
+    nf = E if num_ffn_experts is None else num_ffn_experts
+    idx = np.where(idx >= nf, -1 - (idx - nf), idx).astype(np.int32)
+    return idx, scales, biased
+
+
 def fastep_expand_plan(idx, E):
     idx = _i32(idx)
     T, k = idx.shape

@@ -16,6 +16,7 @@
 #include "src/scheduler/global_reducer.cuh"
 #include "src/scheduler/local_reducer.cuh"
 #include "src/scheduler/zero_reducer.cuh"
+#include "src/utils/topk_sigmoid.cuh"
 
 using bf16 = __nv_bfloat16;
 
@@ -160,6 +161,49 @@ void ref_quant_1x128(void* x, long long rows, long long cols, void* q, float* sc
 // executor/activations.cu (ragged form)
 void ref_silu(const void* gate_up, void* act, const int* excl, int num_experts, int inter_x2, int hint) {
   eps::silu_activate<bf16>((const bf16*)gate_up, (bf16*)act, excl, num_experts, inter_x2, hint, 0);
+}
+
+// utils/topk_sigmoid.cu:264-286 (throws for anything but 256 experts / 8 groups / top-8)
+int ref_topk_sigmoid_f32(const float* scores, const float* bias, float* expert_scales, int* expert_indices, int T, int E,
+                         int n_groups, int topk_groups, int topk, float route_scale) {
+  eps::TopkSigmoidParams<float, float, int> p{};
+  p.scores = scores;
+  p.bias = bias;
+  p.expert_scales = expert_scales;
+  p.expert_indices = expert_indices;
+  p.num_tokens = T;
+  p.num_experts = E;
+  p.num_expert_groups = n_groups;
+  p.topk_groups = topk_groups;
+  p.topk = topk;
+  p.route_scale = route_scale;
+  try {
+    eps::topk_sigmoid(p, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+int ref_topk_sigmoid_bf16(const bf16* scores, const float* bias, float* expert_scales, int* expert_indices, int T, int E,
+                          int n_groups, int topk_groups, int topk, float route_scale) {
+  eps::TopkSigmoidParams<bf16, float, int> p{};
+  p.scores = scores;
+  p.bias = bias;
+  p.expert_scales = expert_scales;
+  p.expert_indices = expert_indices;
+  p.num_tokens = T;
+  p.num_experts = E;
+  p.num_expert_groups = n_groups;
+  p.topk_groups = topk_groups;
+  p.topk = topk;
+  p.route_scale = route_scale;
+  try {
+    eps::topk_sigmoid(p, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
 }
 
 }  // extern "C"

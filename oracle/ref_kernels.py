@@ -132,3 +132,17 @@ def silu(gate_up, excl, num_experts, hint):
     lib().ref_silu(_p(gate_up), _p(act), _p(excl), num_experts, two_i, hint)
     _sync()
     return act
+
+
+def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0):
+    """The reference router (utils/topk_sigmoid.cu); returns None for shapes it does not instantiate."""
+    T, E = scores.shape
+    dev = scores.device
+    w = torch.empty((T, topk), dtype=torch.float32, device=dev)
+    idx = torch.empty((T, topk), dtype=torch.int32, device=dev)
+    fn = lib().ref_topk_sigmoid_bf16 if scores.dtype == torch.bfloat16 else lib().ref_topk_sigmoid_f32
+    rc = fn(_p(scores), _p(bias), _p(w), _p(idx), T, E, n_groups, topk_groups, topk, ctypes.c_float(route_scale))
+    if rc != 0:
+        return None
+    _sync()
+    return idx, w

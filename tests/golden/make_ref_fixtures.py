@@ -29,6 +29,20 @@ PLAN_CASES = [
 ]
 
 
+def record_router(out_dir, dev):
+    """Router: the one shape the reference instantiates (256 experts, 8 groups, 4 of them kept, top-8)."""
+    g = torch.Generator().manual_seed(123)
+    scores = torch.randn((96, 256), generator=g)
+    bias = torch.randn(256, generator=g) * 0.1
+    idx, w = ref.topk_sigmoid(scores.to(dev), bias.to(dev), 8, 4, 8, 2.5)
+    sb = scores.to(torch.bfloat16)
+    idx_b, w_b = ref.topk_sigmoid(sb.to(dev), bias.to(dev), 8, 4, 8, 2.5)
+    np.savez_compressed(os.path.join(out_dir, "ref_router.npz"), scores=scores.numpy(), bias=bias.numpy(),
+                        idx=idx.cpu().numpy(), w=w.cpu().numpy(),
+                        scores_bf16=sb.view(torch.int16).numpy().view(np.uint16), idx_bf16=idx_b.cpu().numpy(),
+                        w_bf16=w_b.cpu().numpy())
+
+
 def main(out_dir):
     os.makedirs(out_dir, exist_ok=True)
     dev = torch.device("cuda:0")
@@ -95,8 +109,14 @@ def main(out_dir):
     act = ref.silu(gu.to(dev), excl.to(dev), 1, 40)
     np.savez_compressed(os.path.join(out_dir, "ref_silu.npz"), gu=gu.view(torch.int16).numpy().view(np.uint16),
                         act=act.cpu().view(torch.int16).numpy().view(np.uint16))
+    record_router(out_dir, dev)
     print("wrote fixtures to", out_dir, {k: v.shape for k, v in list(blob.items())[:4]})
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    out = sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden"
+    if "--router-only" in sys.argv:      # adds ref_router.npz without re-recording the other files
+        os.makedirs(out, exist_ok=True)
+        record_router(out, torch.device("cuda:0"))
+    else:
+        main(out)

@@ -65,3 +65,24 @@ def test_swiglu_matches_reference_kernel(oracle):
     # the reference uses __expf (a few ulp off expf): allow one bf16 ulp, and require most outputs identical
     assert np.all(np.abs(act - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-30)
     assert np.mean(act == ref) > 0.99
+
+
+def test_router_matches_reference_kernel(oracle):
+    """The oracle's router against vectors recorded from the reference's topk_sigmoid kernel on a B200.  The device's
+    expf and numpy's exp may differ in the last place, so the scales are compared to a few ulp and a differing index
+    must sit at a tie of the biased scores."""
+    if not os.path.exists(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_router.npz")):
+        pytest.skip("tests/golden/ref_router.npz has not been recorded")
+    g = _load("ref_router.npz")
+    for tag, scores in (("", g["scores"]), ("_bf16", oracle.bf16_to_f32(g["scores_bf16"]))):
+        idx, w, biased = oracle.topk_sigmoid(scores, g["bias"], 8, 4, 8, 2.5)
+        ref_idx, ref_w = g["idx" + tag], g["w" + tag]
+        diff = idx != ref_idx
+        if diff.any():
+            rows = np.nonzero(diff)[0]
+            a, b = biased[rows, idx[diff]], biased[rows, ref_idx[diff]]
+            assert np.all(np.abs(a - b) <= 4 * np.finfo(np.float32).eps * np.abs(b))
+        same = ~diff.any(axis=1)
+        assert same.mean() > 0.95
+        assert np.allclose(w[same], ref_w[same], rtol=2e-6, atol=0)
+

@@ -25,6 +25,9 @@ def test_ops_are_registered_with_reference_names(ex_ops):
         t = torch.zeros(1)
         ex_ops.aok_run(h, t, t, t, t, 0, 0, t)
     ex_ops.aok_destroy(h)
+    # the router sits in the reference's `utils` library (src/utils/bindings/bindings.cpp:6-9) with ten arguments
+    schema = str(torch.ops.utils.topk_sigmoid.default._schema)
+    assert schema.count("Tensor") == 4 and schema.count("int") == 5 and "float" in schema
 
 
 @pytest.mark.gpu
@@ -58,3 +61,21 @@ def test_torch_ops_run_on_gpu(cuda, oracle, ex_ops):
     assert np.max(np.abs(C.float().cpu().numpy() - want)) <= 2e-2 * np.sqrt(np.mean(want ** 2))
     with pytest.raises(RuntimeError, match="not divisible by 128"):
         ex_ops.aok_run_fp8(0, dv(A)[:, :100].contiguous(), dv(a_s), dv(wq)[:, :, :100].contiguous(), dv(w_s), C, dv(ex), 100, 100, C)
+
+
+@pytest.mark.gpu
+def test_torch_router_op(cuda, ex_ops):
+    from eps_b200 import ops
+
+    gen = torch.Generator().manual_seed(11)
+    scores = torch.randn((40, 256), generator=gen).to(torch.bfloat16).to(cuda)
+    bias = (torch.randn(256, generator=gen) * 0.1).to(cuda)
+    w = torch.empty((40, 8), dtype=torch.float32, device=cuda)
+    idx = torch.empty((40, 8), dtype=torch.int32, device=cuda)
+    torch.ops.utils.topk_sigmoid(scores, bias, w, idx, 40, 256, 8, 4, 8, 2.5)
+    idx2, w2 = ops.topk_sigmoid(scores, bias, 8, 4, 8, 2.5)
+    torch.cuda.synchronize()
+    assert torch.equal(idx, idx2) and torch.equal(w, w2)
+    with pytest.raises(RuntimeError, match="Not supported expert_indices data type"):
+        torch.ops.utils.topk_sigmoid(scores, bias, w, idx.to(torch.int64), 40, 256, 8, 4, 8, 2.5)
+
