@@ -13,8 +13,9 @@
 // power-of-two tile sizes).  Outputs are in selection order.  Ids >= num_ffn_experts can be mapped to the
 // negative ids the scheduler reads as identity experts (-1 - (id - num_ffn_experts)).
 //
-// One warp per token; lane r holds experts [r*E/32, (r+1)*E/32) in registers; every reduction is a warp
-// arg-max on (score, lowest index).
+// One warp per token; lane r holds experts [r*E/32, (r+1)*E/32) in registers (the kernel is instantiated per
+// E/32); every reduction is an arg-max on (score, lowest index), over the warp, or over lane segments for all
+// groups at once when a group is a power-of-two number of whole lanes.
 #include <cfloat>
 
 #include "common.cuh"
@@ -52,83 +53,112 @@ __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <typename T>
+// (higher score, then lower index) over aligned segments of `width` lanes (a power of two); every lane of a
+// segment gets its segment's winner.
+__device__ __forceinline__ Best segment_argmax(Best b, int width) {
+  for (int off = width >> 1; off > 0; off >>= 1) {
+    const float s = __shfl_xor_sync(0xffffffffu, b.score, off);
+    const int i = __shfl_xor_sync(0xffffffffu, b.index, off);
+    if (s > b.score || (s == b.score && i < b.index)) {
+      b.score = s;
+      b.index = i;
+    }
+  }
+  return b;
+}
+
+// kEpt = experts per lane (E / 32), a compile-time bound so that the scores stay in registers.
+template <typename T, int kEpt>
 __global__ void __launch_bounds__(kRouterThreads)
-router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict__ bias, int num_tokens, int E,
-                           int n_groups, int topk_groups, int k, float route_scale, int num_ffn_experts,
+router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict__ bias, int num_tokens, int n_groups,
+                           int topk_groups, int k, float route_scale, int num_ffn_experts,
                            int32_t* __restrict__ out_idx, float* __restrict__ out_w) {
+  constexpr int E = 32 * kEpt;
   const int lane = threadIdx.x & 31;
   const int warps_per_block = kRouterThreads / 32;
-  const int ept = E / 32;            // experts per lane
   const int gsize = E / n_groups;    // experts per group
-  const int e0 = lane * ept;
-  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < num_tokens; t += gridDim.x * warps_per_block) {
-    float orig[kMaxPerLane], biased[kMaxPerLane];
+  const int e0 = lane * kEpt;
+  // Groups made of whole lanes, a power of two of them: all groups are reduced at once inside lane segments.
+  const int lanes_per_group = gsize / kEpt;
+  const bool segmented = gsize % kEpt == 0 && lanes_per_group >= 1 && (lanes_per_group & (lanes_per_group - 1)) == 0;
+  float bias_r[kEpt];
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; i++) {
-      if (i < ept) {
-        const float x = to_float(logits[(size_t)t * E + e0 + i]);
-        const float s = 1.0f / (1.0f + expf(-x));
-        orig[i] = s;
-        biased[i] = s + (bias != nullptr ? bias[e0 + i] : 0.0f);
-      } else {
-        orig[i] = 0.0f;
-        biased[i] = -FLT_MAX;
-      }
+  for (int i = 0; i < kEpt; i++) bias_r[i] = bias != nullptr ? bias[e0 + i] : 0.0f;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < num_tokens; t += gridDim.x * warps_per_block) {
+    float orig[kEpt], biased[kEpt];
+#pragma unroll
+    for (int i = 0; i < kEpt; i++) {
+      const float x = to_float(logits[(size_t)t * E + e0 + i]);
+      const float s = 1.0f / (1.0f + expf(-x));
+      orig[i] = s;
+      biased[i] = s + bias_r[i];
     }
     // ---- group scores: lane g ends up holding the score of group g
     float my_group_score = -FLT_MAX;
-    for (int g = 0; g < n_groups; g++) {
-      const int lo = g * gsize, hi = lo + gsize;
+    if (segmented) {
       Best first{-FLT_MAX, INT32_MAX};
 #pragma unroll
-      for (int i = 0; i < kMaxPerLane; i++) {
-        const int e = e0 + i;
-        if (i < ept && e >= lo && e < hi && biased[i] > first.score) first = Best{biased[i], e};
-      }
-      first = warp_argmax(first);
+      for (int i = 0; i < kEpt; i++)
+        if (biased[i] > first.score) first = Best{biased[i], e0 + i};
+      first = segment_argmax(first, lanes_per_group);
       Best second{-FLT_MAX, INT32_MAX};
 #pragma unroll
-      for (int i = 0; i < kMaxPerLane; i++) {
-        const int e = e0 + i;
-        if (i < ept && e >= lo && e < hi && e != first.index && biased[i] > second.score) second = Best{biased[i], e};
+      for (int i = 0; i < kEpt; i++)
+        if (e0 + i != first.index && biased[i] > second.score) second = Best{biased[i], e0 + i};
+      second = segment_argmax(second, lanes_per_group);
+      const float gs = first.score + second.score;        // held by every lane of group lane / lanes_per_group
+      my_group_score = __shfl_sync(0xffffffffu, gs, (lane * lanes_per_group) & 31);
+    } else {
+      for (int g = 0; g < n_groups; g++) {
+        const int lo = g * gsize, hi = lo + gsize;
+        Best first{-FLT_MAX, INT32_MAX};
+#pragma unroll
+        for (int i = 0; i < kEpt; i++) {
+          const int e = e0 + i;
+          if (e >= lo && e < hi && biased[i] > first.score) first = Best{biased[i], e};
+        }
+        first = warp_argmax(first);
+        Best second{-FLT_MAX, INT32_MAX};
+#pragma unroll
+        for (int i = 0; i < kEpt; i++) {
+          const int e = e0 + i;
+          if (e >= lo && e < hi && e != first.index && biased[i] > second.score) second = Best{biased[i], e};
+        }
+        second = warp_argmax(second);
+        if (lane == g) my_group_score = first.score + second.score;
       }
-      second = warp_argmax(second);
-      const float gs = first.score + second.score;
-      if (lane == g) my_group_score = gs;
     }
     // ---- the topk_groups best groups (n_groups <= 32: one per lane)
     uint32_t group_mask = 0;
     for (int r = 0; r < topk_groups; r++) {
-      Best b{(lane < n_groups && !((group_mask >> lane) & 1u)) ? my_group_score : -FLT_MAX,
-             (lane < n_groups && !((group_mask >> lane) & 1u)) ? lane : INT32_MAX};
+      const bool open = lane < n_groups && !((group_mask >> lane) & 1u);
+      Best b{open ? my_group_score : -FLT_MAX, open ? lane : INT32_MAX};
       b = warp_argmax(b);
       if (b.index < n_groups) group_mask |= 1u << b.index;
     }
-    // ---- k experts among the selected groups
+    // experts outside the kept groups leave the contest
+#pragma unroll
+    for (int i = 0; i < kEpt; i++)
+      if (!((group_mask >> ((e0 + i) / gsize)) & 1u)) biased[i] = -FLT_MAX;
+    // ---- k experts among the kept groups
     float sum = 0.0f;
     float my_w = 0.0f;   // lane j keeps the j-th selected expert
     int my_e = 0;
     for (int j = 0; j < k; j++) {
       Best b{-FLT_MAX, INT32_MAX};
 #pragma unroll
-      for (int i = 0; i < kMaxPerLane; i++) {
-        const int e = e0 + i;
-        if (i < ept && ((group_mask >> (e / gsize)) & 1u) && biased[i] > b.score) b = Best{biased[i], e};
-      }
+      for (int i = 0; i < kEpt; i++)
+        if (biased[i] > b.score) b = Best{biased[i], e0 + i};
       b = warp_argmax(b);
       float o = 0.0f;
-      if (b.index != INT32_MAX && b.index >= e0 && b.index < e0 + ept) {
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; i++)
-          if (i == b.index - e0) {
-            o = orig[i];
-            biased[i] = -FLT_MAX;
-          }
-      }
+      for (int i = 0; i < kEpt; i++)
+        if (e0 + i == b.index) {
+          o = orig[i];
+          biased[i] = -FLT_MAX;
+        }
       // the owner lane holds the unbiased score: hand it to everybody
-      const int owner = b.index != INT32_MAX ? b.index / ept : 0;
-      o = __shfl_sync(0xffffffffu, o, owner);
+      o = __shfl_sync(0xffffffffu, o, b.index != INT32_MAX ? b.index / kEpt : 0);
       sum += o;
       if (lane == j) {
         my_w = o;
@@ -143,6 +173,30 @@ router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict
       out_w[(size_t)t * k + lane] = my_w * rescale;
     }
   }
+}
+
+template <typename T>
+int launch_router(int ept, int blocks, cudaStream_t st, const T* logits, const float* bias, int num_tokens, int n_groups,
+                  int topk_groups, int k, float route_scale, int num_ffn, int32_t* out_idx, float* out_w) {
+#define EPSB_ROUTER_CASE(N)                                                                                          \
+  case N:                                                                                                             \
+    router_topk_sigmoid_kernel<T, N><<<blocks, kRouterThreads, 0, st>>>(logits, bias, num_tokens, n_groups,           \
+                                                                          topk_groups, k, route_scale, num_ffn,       \
+                                                                          out_idx, out_w);                            \
+    break;
+  switch (ept) {
+    EPSB_ROUTER_CASE(1) EPSB_ROUTER_CASE(2) EPSB_ROUTER_CASE(3) EPSB_ROUTER_CASE(4) EPSB_ROUTER_CASE(5)
+    EPSB_ROUTER_CASE(6) EPSB_ROUTER_CASE(7) EPSB_ROUTER_CASE(8) EPSB_ROUTER_CASE(9) EPSB_ROUTER_CASE(10)
+    EPSB_ROUTER_CASE(11) EPSB_ROUTER_CASE(12) EPSB_ROUTER_CASE(13) EPSB_ROUTER_CASE(14) EPSB_ROUTER_CASE(15)
+    EPSB_ROUTER_CASE(16) EPSB_ROUTER_CASE(17) EPSB_ROUTER_CASE(18) EPSB_ROUTER_CASE(19) EPSB_ROUTER_CASE(20)
+    EPSB_ROUTER_CASE(21) EPSB_ROUTER_CASE(22) EPSB_ROUTER_CASE(23) EPSB_ROUTER_CASE(24) EPSB_ROUTER_CASE(25)
+    EPSB_ROUTER_CASE(26) EPSB_ROUTER_CASE(27) EPSB_ROUTER_CASE(28) EPSB_ROUTER_CASE(29) EPSB_ROUTER_CASE(30)
+    EPSB_ROUTER_CASE(31) EPSB_ROUTER_CASE(32)
+    default:
+      return fail(EPSB_ERR_INVALID, "Not supported num_experts: %d", ept * 32);
+  }
+#undef EPSB_ROUTER_CASE
+  return check_launch("router_topk_sigmoid");
 }
 
 }  // namespace
@@ -173,12 +227,10 @@ extern "C" int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16,
   if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
   auto st = static_cast<cudaStream_t>(stream);
   if (logits_are_bf16)
-    router_topk_sigmoid_kernel<__nv_bfloat16><<<(int)blocks, kRouterThreads, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(logits), bias, num_tokens, num_experts, num_expert_groups, topk_groups, topk,
-        route_scale, num_ffn_experts, expert_indices, expert_scales);
-  else
-    router_topk_sigmoid_kernel<float><<<(int)blocks, kRouterThreads, 0, st>>>(
-        static_cast<const float*>(logits), bias, num_tokens, num_experts, num_expert_groups, topk_groups, topk,
-        route_scale, num_ffn_experts, expert_indices, expert_scales);
-  return check_launch("router_topk_sigmoid");
+    return launch_router(num_experts / 32, (int)blocks, st, static_cast<const __nv_bfloat16*>(logits), bias, num_tokens,
+                         num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, expert_indices,
+                         expert_scales);
+  return launch_router(num_experts / 32, (int)blocks, st, static_cast<const float*>(logits), bias, num_tokens,
+                       num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, expert_indices,
+                       expert_scales);
 }
