@@ -109,9 +109,27 @@ void topk_sigmoid_op(at::Tensor scores, at::Tensor bias, at::Tensor expert_scale
                                     expert_scales.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// utils.rms_norm_op with the reference's argument list (src/utils/bindings/th_rms_norm.cu:13-35)
+void rms_norm_op(at::Tensor output, at::Tensor input, at::Tensor scale, double eps) {
+  if (output.dim() != 2 || input.dim() != 2)
+    throw std::runtime_error("output and input dim must be 2 but got " + std::to_string(output.dim()) + " and " +
+                             std::to_string(input.dim()));
+  check(output, 2, "output");
+  check(input, 2, "input");
+  check(scale, 1, "scale");
+  TORCH_CHECK(output.scalar_type() == at::kBFloat16 && input.scalar_type() == at::kBFloat16 &&
+                  scale.scalar_type() == at::kBFloat16,
+              "output, input and scale must be bfloat16");
+  raise_if(epsb_rms_norm(output.data_ptr(), input.data_ptr(), scale.data_ptr(), (float)eps, input.size(0),
+                         input.size(1), at::cuda::getCurrentCUDAStream().stream()));
+}
+
 }  // namespace
 
-TORCH_LIBRARY(utils, m) { m.def("topk_sigmoid", &topk_sigmoid_op); }
+TORCH_LIBRARY(utils, m) {
+  m.def("topk_sigmoid", &topk_sigmoid_op);
+  m.def("rms_norm_op", &rms_norm_op);
+}
 
 TORCH_LIBRARY(executor, m) {
   m.def("aok_create", &aok_create);

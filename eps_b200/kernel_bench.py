@@ -87,6 +87,13 @@ def main():
     for name, nbytes, ms in out:
         print(json.dumps({"kernel": name, "algorithmic_bytes": nbytes, "ms": ms, "GB_per_s": nbytes / ms / 1e6}))
 
+    xn = torch.randn((R, H), device=dev, dtype=torch.bfloat16)
+    scn = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    on = torch.empty_like(xn)
+    ms = _time(lambda: ops.rms_norm(xn, scn, 1e-6, out=on), a.iters)
+    print(json.dumps({"kernel": "rms_norm (bf16 rows)", "algorithmic_bytes": 4.0 * R * H, "ms": ms,
+                      "GB_per_s": 4.0 * R * H / ms / 1e6}))
+
     # router: T tokens x `--experts` logits, 8 groups of which 4 stay, top-k
     logits = torch.randn((T, a.experts), device=dev, dtype=torch.bfloat16)
     rbias = torch.randn(a.experts, device=dev) * 0.1

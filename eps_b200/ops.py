@@ -282,6 +282,21 @@ def topk_sigmoid(scores, bias, num_expert_groups, topk_groups, topk, route_scale
     return expert_indices, expert_scales
 
 
+def rms_norm(input, scale, eps, out=None):
+    """out = (input * rsqrt(mean(input^2, dim=1) + eps)) * scale, bf16 rows (reference utils.rms_norm_op)."""
+    _check(input, "input", torch.bfloat16, 2)
+    _check(scale, "scale", torch.bfloat16, 1)
+    m, n = input.shape
+    if scale.numel() != n:
+        raise EpsError(f"scale must have {n} entries")
+    if out is None:
+        out = torch.empty_like(input)
+    else:
+        _check(out, "output", torch.bfloat16, 2)
+    call("epsb_rms_norm", ptr(out), ptr(input), ptr(scale), float(eps), m, n, stream_ptr())
+    return out
+
+
 def plan_set_max_cluster(max_ctas: int) -> None:
     """CTAs (1, 2, 4 or 8) the plan kernels may use from now on."""
     call("epsb_plan_set_max_cluster", int(max_ctas))

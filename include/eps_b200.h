@@ -87,6 +87,15 @@ int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16, const floa
                              int num_experts, int num_expert_groups, int topk_groups, int topk, float route_scale,
                              int num_ffn_experts, int32_t* expert_indices, float* expert_scales, void* stream);
 
+/* ----------------------------------------------------------------------------
+ * RMS normalisation of bf16 rows (a caller of the path in a full model):
+ *   out[r, c] = bf16( (x[r, c] * rsqrt(mean_c(x[r, :]^2) + eps)) * scale[c] ), fp32 arithmetic.
+ * ref: rms_norm (src/utils/rms_norm.cu:103-140), torch op utils.rms_norm_op
+ *      (src/utils/bindings/th_rms_norm.cu:13-35).  n must be even ("dim ... is
+ *      not divisible by 2.", as the reference).  out, input [m, n] bf16, scale [n] bf16.
+ * -------------------------------------------------------------------------- */
+int epsb_rms_norm(void* out, const void* input, const void* scale, float eps, int64_t m, int64_t n, void* stream);
+
 /* CTAs a plan kernel may use (a thread-block cluster of 1, 2, 4 or 8; default 8, chosen per call from the item
  * count).  No counterpart in the reference, whose plan kernels are single CTAs.  Process-wide; a caller that
  * runs a plan next to a kernel occupying almost every SM sets 1, because a cluster only starts once all of its

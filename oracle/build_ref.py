@@ -28,6 +28,7 @@ REF_SOURCES = [
     "src/quant/fp8.cu",
     "src/common/debug.cu",
     "src/utils/topk_sigmoid.cu",
+    "src/utils/rms_norm.cu",
 ]
 
 

@@ -232,6 +232,19 @@ def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0, num
     return idx, scales, biased
 
 
+def rms_norm(x_bits, scale_bits, eps):
+    """RMS normalisation of bf16 rows, restating reference src/utils/rms_norm.cu:103-140: the sum of squares in fp32
+    (here accumulated in float64 and rounded once: the reference's order is a block reduction), inv = rsqrt(.5 * sum
+    / (n/2) + eps) in fp32, out = bf16((x * inv) * scale).  -> bf16 bits [m, n]."""
+    x = bf16_to_f32(np.asarray(x_bits))
+    sc = bf16_to_f32(np.asarray(scale_bits))
+    n = x.shape[1]
+    total = (x.astype(np.float64) ** 2).sum(axis=1).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt(np.float32(0.5) * total / np.float32(n // 2) + np.float32(eps), dtype=np.float32))
+    out = ((x * inv.astype(np.float32)[:, None]).astype(np.float32) * sc[None, :]).astype(np.float32)
+    return bf16_bits(out)
+
+
 def fastep_expand_plan(idx, E):
     idx = _i32(idx)
     T, k = idx.shape

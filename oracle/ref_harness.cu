@@ -16,6 +16,7 @@
 #include "src/scheduler/global_reducer.cuh"
 #include "src/scheduler/local_reducer.cuh"
 #include "src/scheduler/zero_reducer.cuh"
+#include "src/utils/rms_norm.cuh"
 #include "src/utils/topk_sigmoid.cuh"
 
 using bf16 = __nv_bfloat16;
@@ -200,6 +201,16 @@ int ref_topk_sigmoid_bf16(const bf16* scores, const float* bias, float* expert_s
   p.route_scale = route_scale;
   try {
     eps::topk_sigmoid(p, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+// utils/rms_norm.cu:128-140
+int ref_rms_norm_bf16(bf16* out, const bf16* input, const bf16* scale, float eps, int m, int n) {
+  try {
+    eps::rms_norm<bf16>(out, input, scale, eps, m, n, 0);
   } catch (...) {
     return 1;
   }

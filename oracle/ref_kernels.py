@@ -146,3 +146,14 @@ def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0):
         return None
     _sync()
     return idx, w
+
+
+def rms_norm(x, scale, eps):
+    """The reference rms_norm on bf16 rows; None if it refuses the shape (odd row length)."""
+    out = torch.empty_like(x)
+    rc = lib().ref_rms_norm_bf16(_p(out), _p(x), _p(scale), ctypes.c_float(eps), x.shape[0], x.shape[1])
+    if rc != 0:
+        return None
+    _sync()
+    return out
+

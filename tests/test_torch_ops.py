@@ -79,3 +79,17 @@ def test_torch_router_op(cuda, ex_ops):
     with pytest.raises(RuntimeError, match="Not supported expert_indices data type"):
         torch.ops.utils.topk_sigmoid(scores, bias, w, idx.to(torch.int64), 40, 256, 8, 4, 8, 2.5)
 
+
+@pytest.mark.gpu
+def test_torch_rms_norm_op(cuda, ex_ops):
+    from eps_b200 import ops
+
+    x = torch.randn((9, 512), generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(cuda)
+    sc = torch.ones(512, dtype=torch.bfloat16, device=cuda)
+    out = torch.empty_like(x)
+    torch.ops.utils.rms_norm_op(out, x, sc, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ops.rms_norm(x, sc, 1e-6))
+    with pytest.raises(RuntimeError, match="dim must be 2"):
+        torch.ops.utils.rms_norm_op(out, x[0], sc, 1e-6)
+
