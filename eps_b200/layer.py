@@ -88,13 +88,21 @@ class MoELayerFP8:
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 ops.gemm_set_sm_count(max(self.num_sms - 4, 1))
-                shared_out = self._shared_expert(xq, xs, T)
-                ops.gemm_set_sm_count(0)
+                try:
+                    shared_out = self._shared_expert(xq, xs, T)
+                finally:
+                    ops.gemm_set_sm_count(0)
                 shared_done = torch.cuda.Event()
                 shared_done.record(side)
         # next to the shared expert's GEMMs (which occupy all but four SMs) a plan must fit into single free SMs
-        ops.plan_set_max_cluster(1 if shared_done is not None else 8)
-        excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1)
+        if shared_done is not None:
+            ops.plan_set_max_cluster(1)
+        try:
+            excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True,
+                                                     host_sync=self.W > 1)
+        finally:
+            if shared_done is not None:
+                ops.plan_set_max_cluster(8)   # the limit is process-wide: leave the default behind
         n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
         rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)
         if rows_k > self.max_gemm_rows:
