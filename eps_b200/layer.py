@@ -176,6 +176,16 @@ class MoELayerFP8:
         self.kernel_launches = n
         return out
 
+    def forward_routed(self, x: torch.Tensor, router_logits: torch.Tensor, router_bias: torch.Tensor | None,
+                       num_expert_groups: int = 1, topk_groups: int = 1, route_scale: float = 1.0,
+                       num_zero_experts: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The layer fed by the router: router_logits [T, num_experts + num_zero_experts] (fp32 or bf16) go through
+        topk_sigmoid (reference utils/topk_sigmoid), whose indices and weights are what `forward` reads; the last
+        num_zero_experts ids are identity experts."""
+        idx, w = ops.topk_sigmoid(router_logits, router_bias, num_expert_groups, topk_groups, self.k, route_scale,
+                                  num_ffn_experts=router_logits.shape[1] - num_zero_experts)
+        return self.forward(x, idx, w, out=out)
+
     def _shared_expert(self, xq, xs, T):
         """The always-on expert on the quantised tokens; returns its [T, H] bf16 output (None without one)."""
         if self.shared is None or T == 0:

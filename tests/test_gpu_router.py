@@ -95,6 +95,36 @@ def test_router_feeds_the_plans(cuda, oracle):
     assert np.array_equal(zero.cpu().numpy(), oracle.zero_plan(idx.cpu().numpy(), w.cpu().numpy()))
 
 
+def test_layer_fed_by_the_router(cuda, oracle):
+    """forward_routed == router + forward, and both match the fp32 oracle run on the oracle's own routing."""
+    from eps_b200 import ops, workloads
+    from eps_b200.layer import MoELayerFP8
+
+    T, H, I, E, k, nz = 48, 512, 256, 32, 4, 32
+    cfg = workloads.CONFIGS[0].scaled(tokens_per_rank=T, hidden=H, inter=I, num_experts=E, top_k=k)
+    x = workloads.make_tokens(cfg)
+    gu = torch.stack([workloads.make_expert_weights(cfg, e)[0] for e in range(E)])
+    d = torch.stack([workloads.make_expert_weights(cfg, e)[1] for e in range(E)])
+    gq, gs = ops.quant_block128(gu.to(cuda))
+    dq, ds = ops.quant_block128(d.to(cuda))
+    layer = MoELayerFP8(H, I, E, k, T, gq, gs, dq, ds)
+    gen = torch.Generator().manual_seed(9)
+    logits = torch.randn((T, E + nz), generator=gen)
+    bias = torch.randn(E + nz, generator=gen) * 0.1
+    out = layer.forward_routed(x.to(cuda), logits.to(cuda), bias.to(cuda), 4, 2, 1.5, num_zero_experts=nz)
+    idx, w = ops.topk_sigmoid(logits.to(cuda), bias.to(cuda), 4, 2, k, 1.5, num_ffn_experts=E)
+    out2 = layer.forward(x.to(cuda), idx, w)
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert torch.equal(out, out2)
+    assert (idx < 0).any() and (idx >= 0).any()      # both identity and FFN experts are routed to
+    want = oracle.moe_layer_fp32(x.view(torch.int16).numpy().view(np.uint16), idx.cpu().numpy(), w.cpu().numpy(),
+                                 *oracle.quant_block128(gu.float().numpy()), *oracle.quant_block128(d.float().numpy()))
+    got = out.float().cpu().numpy()
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    assert np.all(np.abs(got - want) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want))
+
+
 def test_router_errors(cuda):
     from eps_b200 import ops
     from eps_b200._lib import EpsError
