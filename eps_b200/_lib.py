@@ -45,6 +45,7 @@ SIGNATURES = {
     "epsb_plan_set_max_cluster": [_I],
     "epsb_rms_norm": [_P, _P, _P, c_float, _L, _L, _P],
     "epsb_router_topk_sigmoid": [_P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
+    "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_gather_row_weights": [_P, _P, _P, _I, _L, _P, _P],
 }
 

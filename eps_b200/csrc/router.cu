@@ -3,7 +3,7 @@
 // Semantics of the reference's topk_sigmoid (src/utils/topk_sigmoid.cu:158-262), which it instantiates for
 // 256 experts / 8 groups / top-8 only; here for any expert count that is a multiple of 32 up to 1024, any
 // group count that divides it, any k <= 32:
-//   score  = 1 / (1 + expf(-logit))                      (fp32)
+//   score  = 1 / (1 + expf(-logit))                      (fp32; or, not in the reference, softmax over the token's logits)
 //   biased = score + bias[e]
 //   group score = sum of the two largest biased scores of the group        (topk_sigmoid.cu:65-102)
 //   the topk_groups groups with the largest group score stay               (:104-118)
@@ -71,7 +71,7 @@ __device__ __forceinline__ Best segment_argmax(Best b, int width) {
 template <typename T, int kEpt>
 __global__ void __launch_bounds__(kRouterThreads)
 router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict__ bias, int num_tokens, int n_groups,
-                           int topk_groups, int k, float route_scale, int num_ffn_experts,
+                           int topk_groups, int k, float route_scale, int num_ffn_experts, int softmax,
                            int32_t* __restrict__ out_idx, float* __restrict__ out_w) {
   constexpr int E = 32 * kEpt;
   const int lane = threadIdx.x & 31;
@@ -86,12 +86,36 @@ router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict
   for (int i = 0; i < kEpt; i++) bias_r[i] = bias != nullptr ? bias[e0 + i] : 0.0f;
   for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < num_tokens; t += gridDim.x * warps_per_block) {
     float orig[kEpt], biased[kEpt];
+    if (softmax) {   // warp-uniform: score = softmax over all experts of the token
+      float mx = -FLT_MAX;
 #pragma unroll
-    for (int i = 0; i < kEpt; i++) {
-      const float x = to_float(logits[(size_t)t * E + e0 + i]);
-      const float s = 1.0f / (1.0f + expf(-x));
-      orig[i] = s;
-      biased[i] = s + bias_r[i];
+      for (int i = 0; i < kEpt; i++) {
+        orig[i] = to_float(logits[(size_t)t * E + e0 + i]);
+        mx = fmaxf(mx, orig[i]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      float den = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kEpt; i++) {
+        orig[i] = expf(orig[i] - mx);
+        den += orig[i];
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+#pragma unroll
+      for (int i = 0; i < kEpt; i++) {
+        orig[i] = orig[i] / den;
+        biased[i] = orig[i] + bias_r[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kEpt; i++) {
+        const float x = to_float(logits[(size_t)t * E + e0 + i]);
+        const float s = 1.0f / (1.0f + expf(-x));
+        orig[i] = s;
+        biased[i] = s + bias_r[i];
+      }
     }
     // ---- group scores: lane g ends up holding the score of group g
     float my_group_score = -FLT_MAX;
@@ -177,12 +201,12 @@ router_topk_sigmoid_kernel(const T* __restrict__ logits, const float* __restrict
 
 template <typename T>
 int launch_router(int ept, int blocks, cudaStream_t st, const T* logits, const float* bias, int num_tokens, int n_groups,
-                  int topk_groups, int k, float route_scale, int num_ffn, int32_t* out_idx, float* out_w) {
+                  int topk_groups, int k, float route_scale, int num_ffn, int softmax, int32_t* out_idx, float* out_w) {
 #define EPSB_ROUTER_CASE(N)                                                                                          \
   case N:                                                                                                             \
     router_topk_sigmoid_kernel<T, N><<<blocks, kRouterThreads, 0, st>>>(logits, bias, num_tokens, n_groups,           \
                                                                           topk_groups, k, route_scale, num_ffn,       \
-                                                                          out_idx, out_w);                            \
+                                                                          softmax, out_idx, out_w);                   \
     break;
   switch (ept) {
     EPSB_ROUTER_CASE(1) EPSB_ROUTER_CASE(2) EPSB_ROUTER_CASE(3) EPSB_ROUTER_CASE(4) EPSB_ROUTER_CASE(5)
@@ -205,10 +229,12 @@ int launch_router(int ept, int blocks, cudaStream_t st, const T* logits, const f
 
 using namespace epsb;
 
-extern "C" int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16, const float* bias, int num_tokens,
-                                        int num_experts, int num_expert_groups, int topk_groups, int topk,
-                                        float route_scale, int num_ffn_experts, int32_t* expert_indices,
-                                        float* expert_scales, void* stream) {
+extern "C" int epsb_router_topk(int score_func, const void* logits, int logits_are_bf16, const float* bias,
+                                int num_tokens, int num_experts, int num_expert_groups, int topk_groups, int topk,
+                                float route_scale, int num_ffn_experts, int32_t* expert_indices, float* expert_scales,
+                                void* stream) {
+  EPSB_REQUIRE(score_func == EPSB_ROUTER_SIGMOID || score_func == EPSB_ROUTER_SOFTMAX, EPSB_ERR_INVALID,
+               "unknown score function %d", score_func);
   EPSB_REQUIRE(num_tokens >= 0, EPSB_ERR_INVALID, "num_tokens %d is negative", num_tokens);
   EPSB_REQUIRE(num_experts > 0 && num_experts % 32 == 0 && num_experts <= 32 * kMaxPerLane, EPSB_ERR_INVALID,
                "Not supported num_experts: %d (a multiple of 32 up to %d)", num_experts, 32 * kMaxPerLane);
@@ -228,9 +254,18 @@ extern "C" int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16,
   auto st = static_cast<cudaStream_t>(stream);
   if (logits_are_bf16)
     return launch_router(num_experts / 32, (int)blocks, st, static_cast<const __nv_bfloat16*>(logits), bias, num_tokens,
-                         num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, expert_indices,
-                         expert_scales);
+                         num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, score_func,
+                         expert_indices, expert_scales);
   return launch_router(num_experts / 32, (int)blocks, st, static_cast<const float*>(logits), bias, num_tokens,
-                       num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, expert_indices,
+                       num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, score_func, expert_indices,
                        expert_scales);
+}
+
+extern "C" int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16, const float* bias, int num_tokens,
+                                        int num_experts, int num_expert_groups, int topk_groups, int topk,
+                                        float route_scale, int num_ffn_experts, int32_t* expert_indices,
+                                        float* expert_scales, void* stream) {
+  return epsb_router_topk(EPSB_ROUTER_SIGMOID, logits, logits_are_bf16, bias, num_tokens, num_experts,
+                          num_expert_groups, topk_groups, topk, route_scale, num_ffn_experts, expert_indices,
+                          expert_scales, stream);
 }

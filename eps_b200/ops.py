@@ -260,7 +260,7 @@ def gemm_set_sm_count(sm_count: int) -> None:
 
 
 def topk_sigmoid(scores, bias, num_expert_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None,
-                 expert_indices=None, expert_scales=None):
+                 expert_indices=None, expert_scales=None, score_func="sigmoid"):
     """Router (reference utils/topk_sigmoid): scores [T, E] fp32 or bf16 logits, bias [E] fp32 or None ->
     (expert_indices [T, topk] int32, expert_scales [T, topk] fp32) in the layout the Scheduler reads."""
     if scores.dtype not in (torch.float32, torch.bfloat16):
@@ -276,7 +276,9 @@ def topk_sigmoid(scores, bias, num_expert_groups, topk_groups, topk, route_scale
         expert_indices = torch.empty((T, topk), dtype=torch.int32, device=dev)
     if expert_scales is None:
         expert_scales = torch.empty((T, topk), dtype=torch.float32, device=dev)
-    call("epsb_router_topk_sigmoid", ptr(scores), int(scores.dtype == torch.bfloat16), ptr(bias), T, E,
+    if score_func not in ("sigmoid", "softmax"):
+        raise EpsError(f"score_func must be 'sigmoid' or 'softmax', got {score_func!r}")
+    call("epsb_router_topk", int(score_func == "softmax"), ptr(scores), int(scores.dtype == torch.bfloat16), ptr(bias), T, E,
          int(num_expert_groups), int(topk_groups), int(topk), float(route_scale),
          int(E if num_ffn_experts is None else num_ffn_experts), ptr(expert_indices), ptr(expert_scales), stream_ptr())
     return expert_indices, expert_scales

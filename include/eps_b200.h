@@ -87,6 +87,15 @@ int epsb_router_topk_sigmoid(const void* logits, int logits_are_bf16, const floa
                              int num_experts, int num_expert_groups, int topk_groups, int topk, float route_scale,
                              int num_ffn_experts, int32_t* expert_indices, float* expert_scales, void* stream);
 
+/* The same selection with a choice of score function.  EPSB_ROUTER_SOFTMAX (no counterpart in the reference, whose
+ * router is sigmoid only): score = expf(logit - max) / sum over the token's experts; everything after the score
+ * (bias, groups, top-k, renormalisation of the chosen scores to route_scale) as above. */
+#define EPSB_ROUTER_SIGMOID 0
+#define EPSB_ROUTER_SOFTMAX 1
+int epsb_router_topk(int score_func, const void* logits, int logits_are_bf16, const float* bias, int num_tokens,
+                     int num_experts, int num_expert_groups, int topk_groups, int topk, float route_scale,
+                     int num_ffn_experts, int32_t* expert_indices, float* expert_scales, void* stream);
+
 /* ----------------------------------------------------------------------------
  * RMS normalisation of bf16 rows (a caller of the path in a full model):
  *   out[r, c] = bf16( (x[r, c] * rsqrt(mean_c(x[r, :]^2) + eps)) * scale[c] ), fp32 arithmetic.

@@ -192,7 +192,8 @@ def zero_plan(idx, w):
     return z[:T]
 
 
-def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None):
+def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None,
+                 score_func="sigmoid"):
     """Router, restating reference src/utils/topk_sigmoid.cu:158-262 in fp32 numpy (vectorised over tokens).
 
     score = 1/(1+exp(-x)) (:181-184 `sigmoid`, fp32), biased = score + bias (:211-216); group score = sum of the
@@ -205,7 +206,11 @@ def topk_sigmoid(scores, bias, n_groups, topk_groups, topk, route_scale=1.0, num
     x = np.asarray(scores, dtype=np.float32)
     T, E = x.shape
     one = np.float32(1.0)
-    orig = (one / (one + np.exp(-x, dtype=np.float32))).astype(np.float32)
+    if score_func == "softmax":   # not in the reference: softmax over the token's logits, fp32
+        ex = np.exp(x - x.max(axis=1, keepdims=True), dtype=np.float32)
+        orig = (ex / ex.sum(axis=1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    else:
+        orig = (one / (one + np.exp(-x, dtype=np.float32))).astype(np.float32)
     biased = orig if bias is None else (orig + np.asarray(bias, dtype=np.float32)[None, :]).astype(np.float32)
     gsize = E // n_groups
     neg = np.float32(-np.finfo(np.float32).max)

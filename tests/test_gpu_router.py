@@ -95,6 +95,31 @@ def test_router_feeds_the_plans(cuda, oracle):
     assert np.array_equal(zero.cpu().numpy(), oracle.zero_plan(idx.cpu().numpy(), w.cpu().numpy()))
 
 
+@pytest.mark.parametrize("T,E,k", [(128, 128, 8), (64, 256, 8), (40, 512, 12)])
+def test_router_softmax_matches_torch_topk(cuda, oracle, T, E, k):
+    """Softmax scores, no groups, no bias: the plain top-k softmax router (what eps_b200.workloads generates its
+    routing with): indices == torch.topk, weights == softmax probabilities renormalised over the chosen experts."""
+    from eps_b200 import ops
+
+    gen = torch.Generator().manual_seed(E + k)
+    logits = torch.randn((T, E), generator=gen)
+    idx, w = ops.topk_sigmoid(logits.to(cuda), None, 1, 1, k, 1.0, score_func="softmax")
+    torch.cuda.synchronize()
+    top = torch.topk(logits, k, dim=1)
+    probs = torch.softmax(logits, dim=1).gather(1, top.indices)
+    want_w = probs / probs.sum(dim=1, keepdim=True)
+    assert torch.equal(idx.cpu().long(), top.indices)
+    assert torch.allclose(w.cpu(), want_w, rtol=1e-5, atol=1e-8)
+    oi, ow, _ = oracle.topk_sigmoid(logits.numpy(), None, 1, 1, k, 1.0, score_func="softmax")
+    assert np.array_equal(oi, idx.cpu().numpy()) and np.allclose(ow, w.cpu().numpy(), rtol=1e-5)
+    # with groups and bias the oracle is the checker
+    bias = torch.randn(E, generator=gen) * 0.01
+    idx, w = ops.topk_sigmoid(logits.to(cuda), bias.to(cuda), 8, 4, k, 2.0, score_func="softmax")
+    oi, ow, biased = oracle.topk_sigmoid(logits.numpy(), bias.numpy(), 8, 4, k, 2.0, score_func="softmax")
+    same = (oi == idx.cpu().numpy()).all(axis=1)
+    assert same.mean() > 0.95 and np.allclose(ow[same], w.cpu().numpy()[same], rtol=2e-5)
+
+
 def test_layer_fed_by_the_router(cuda, oracle):
     """forward_routed == router + forward, and both match the fp32 oracle run on the oracle's own routing."""
     from eps_b200 import ops, workloads
