@@ -65,6 +65,7 @@ class MoELayerFP8:
             self.sh_out = torch.empty((T, hidden), dtype=torch.bfloat16, device=dev)
             self._sh_excl = {}
         self.kernel_launches = 0
+        self.shared_sm_reserve = 4   # SMs the shared expert's GEMMs leave to the plan and gather kernels (EP=1)
         self.gateup_events = None  # optional (start, end) torch.cuda.Event pair recorded around the gate/up GEMM
 
     def forward(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor,
@@ -87,7 +88,7 @@ class MoELayerFP8:
             side = self._comm_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                ops.gemm_set_sm_count(max(self.num_sms - 4, 1))
+                ops.gemm_set_sm_count(max(self.num_sms - self.shared_sm_reserve, 1))
                 try:
                     shared_out = self._shared_expert(xq, xs, T)
                 finally:
