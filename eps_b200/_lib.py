@@ -23,10 +23,10 @@ SIGNATURES = {
     "epsb_quant_1x128_ragged": [_P, _P, _I, _L, _P, _P, _L, _I, _P],
     "epsb_dequant_1x128": [_P, _P, _L, _L, _P, _P],
     "epsb_quant_block128": [_P, _L, _L, _L, _P, _P, _P],
-    "epsb_source_plans": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P],
+    "epsb_source_plans": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "epsb_recv_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
-    "epsb_expert_plans": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P],
-    "epsb_expert_plans_noalloc": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P],
+    "epsb_expert_plans": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P],
+    "epsb_expert_plans_noalloc": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _I, _P],
     "epsb_fastep_expand_plan": [_P, _I, _I, _I, _P, _P, _P],
     "epsb_fastep_plan": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "epsb_gather_rows": [_P, _P, _P, c_int32, c_int32, _P, _I, _I, _L, _L, _L, _P],
@@ -39,10 +39,8 @@ SIGNATURES = {
     "epsb_reduce_ep1": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_fastep_reduce": [_P, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_silu_run": [_P, _P, _P, _I, _L, _L, _P],
-    "epsb_grouped_gemm_fp8": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _P, _P],
-    "epsb_grouped_gemm_fp8_tn": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _I, _P],
-    "epsb_gemm_set_sm_count": [_I],
-    "epsb_plan_set_max_cluster": [_I],
+    "epsb_grouped_gemm_fp8": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _P, _I, _P],
+    "epsb_grouped_gemm_fp8_tn": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _I, _I, _P],
     "epsb_rms_norm": [_P, _P, _P, c_float, _L, _L, _P],
     "epsb_router_topk_sigmoid": [_P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],

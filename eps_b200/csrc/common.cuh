@@ -29,8 +29,8 @@ inline int check_launch(const char* what) {
   return EPSB_OK;
 }
 
-// CTAs a persistent GEMM launch may use: every SM, or the count set with epsb_gemm_set_sm_count().
-int gemm_cta_limit();
+// CTAs a persistent GEMM launch may use: every SM, or the caller's sm_count when that is in (0, all).
+int gemm_cta_limit(int sm_count_arg);
 
 inline int sm_count() {
   static int cached[64] = {0};

@@ -586,7 +586,9 @@ using namespace epsb;
 
 extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
                                      const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K,
-                                     void* C, float* c_s, const float* row_w, int32_t* status, void* stream) {
+                                     void* C, float* c_s, const float* row_w, int32_t* status, int sm_count,
+                                     void* stream) {
+  EPSB_REQUIRE(sm_count >= 0, EPSB_ERR_INVALID, "sm_count %d is negative", sm_count);
   EPSB_REQUIRE(mode == EPSB_GEMM_PLAIN || mode == EPSB_GEMM_GATEUP || mode == EPSB_GEMM_DOWN, EPSB_ERR_INVALID,
                "unknown GEMM mode %d", mode);
   EPSB_REQUIRE(num_experts > 0 && num_experts <= kMaxExperts, EPSB_ERR_INVALID, "num_experts %d out of range",
@@ -626,7 +628,7 @@ extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, 
   // tile-count upper bound without reading the device-side prefix sum
   const int64_t m_tiles_max = (max_rows + kBM - 1) / kBM + num_experts;
   int64_t grid = m_tiles_max * p.n_tiles;
-  if (grid > gemm_cta_limit()) grid = gemm_cta_limit();
+  if (grid > gemm_cta_limit(sm_count)) grid = gemm_cta_limit(sm_count);
   auto st = static_cast<cudaStream_t>(stream);
   switch (mode) {
     case EPSB_GEMM_GATEUP: return launch<EPSB_GEMM_GATEUP>(ta, tb, p, (int)grid, st);

@@ -521,7 +521,7 @@ int make_map_tn(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int
 namespace {
 int launch_grouped_gemm_tn(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
                            const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
-                           const float* row_w, int32_t* status, int tile_tokens, cudaStream_t stream) {
+                           const float* row_w, int32_t* status, int tile_tokens, int sm_count, cudaStream_t stream) {
   EPSB_REQUIRE(tile_tokens >= 16 && tile_tokens <= 256 && tile_tokens % 16 == 0, EPSB_ERR_INVALID,
                "tile_tokens %d must be a multiple of 16 in [16, 256]", tile_tokens);
   TnParams p;
@@ -557,7 +557,7 @@ int launch_grouped_gemm_tn(int mode, const void* A, const float* a_s, const void
   }
   const int64_t tok_tiles_max = (max_rows + tile_tokens - 1) / tile_tokens + num_experts;
   int64_t grid = tok_tiles_max * p.w_tiles;
-  if (grid > gemm_cta_limit()) grid = gemm_cta_limit();
+  if (grid > gemm_cta_limit(sm_count)) grid = gemm_cta_limit(sm_count);
   // kCh: 16-column chunks one column half can hold (sets the epilogue's register arrays)
   const int chunks_per_half = (tile_tokens / 16 + 1) / 2;
   const auto st = stream;
@@ -588,7 +588,9 @@ using namespace epsb;
 
 extern "C" int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
                                         const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K,
-                                        void* C, const float* row_w, int32_t* status, int tile_tokens, void* stream) {
+                                        void* C, const float* row_w, int32_t* status, int tile_tokens, int sm_count,
+                                        void* stream) {
+  EPSB_REQUIRE(sm_count >= 0, EPSB_ERR_INVALID, "sm_count %d is negative", sm_count);
   EPSB_REQUIRE(mode == EPSB_GEMM_PLAIN || mode == EPSB_GEMM_DOWN, EPSB_ERR_INVALID,
                "token-N GEMM supports modes PLAIN and DOWN, got %d", mode);
   EPSB_REQUIRE(num_experts > 0 && num_experts <= kMaxExperts, EPSB_ERR_INVALID, "num_experts %d out of range",
@@ -602,5 +604,5 @@ extern "C" int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_
                "tensor too large for 32-bit TMA coordinates");
   if (max_rows <= 0) return EPSB_OK;
   return launch_grouped_gemm_tn(mode, A, a_s, B, b_s, excl, num_experts, max_rows, N, K, C, row_w, status, tile_tokens,
-                                static_cast<cudaStream_t>(stream));
+                                sm_count, static_cast<cudaStream_t>(stream));
 }

@@ -27,6 +27,7 @@ constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kMaxBuckets = 1024;
 
 constexpr int kMaxCluster = 8;  // portable cluster size
+constexpr int kPlanStatusRowsExceeded = EPSB_PLAN_ROWS_EXCEEDED;
 
 struct SortScratch {
   int32_t* rows;    // [kPlanWarps][B] per-warp counts, then per-warp exclusive offsets inside this CTA
@@ -52,11 +53,10 @@ __device__ __forceinline__ SortScratch carve(int32_t* smem, int B) {
 
 size_t sort_smem_bytes(int B) { return sizeof(int32_t) * ((size_t)kScratchRows * B + kPlanWarps + 2); }
 
-std::atomic<int> g_max_cluster{kMaxCluster};
-
-// CTAs per plan: one per 1024 items, a power of two up to the portable cluster size (or the caller's limit).
-int cluster_size_for(int64_t n_items) {
-  const int limit = g_max_cluster.load(std::memory_order_relaxed);
+// CTAs per plan: one per 1024 items, a power of two up to the portable cluster size or the caller's limit
+// (max_cluster 0 = no limit of the caller's).
+int cluster_size_for(int64_t n_items, int max_cluster = 0) {
+  const int limit = max_cluster > 0 && max_cluster < kMaxCluster ? max_cluster : kMaxCluster;
   int c = 1;
   while (c * 2 <= limit && (int64_t)c * kPlanThreads < n_items) c *= 2;
   return c;
@@ -395,10 +395,25 @@ struct LocalReducePlanProblem {
 __global__ void __launch_bounds__(kPlanThreads, 1)
 expert_plans_kernel(const int32_t* __restrict__ ridx, const int32_t* __restrict__ recv_incl, int k, int lo, int hi,
                     int W, int S, int NT, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm, int32_t* scale_map,
-                    int32_t* red_map, int32_t* ret_incl, int cache_items) {
+                    int32_t* red_map, int32_t* ret_incl, int cache_items, int max_rows, int32_t* status) {
   extern __shared__ int32_t plan_smem[];
   const int EL = hi - lo;
   const int R = recv_incl[W * S - 1];
+  // Every buffer, the shared-memory key cache and the cluster size were sized by the host from max_rows.  A row
+  // count beyond that promise (a corrupted or foreign receive plan) must not be followed: every CTA takes this
+  // same branch, the plans come out empty (no GEMM rows, nothing returned) and the caller's status word says why.
+  if (R < 0 || R > max_rows) {
+    if (cluster_leader()) {
+      for (int e = threadIdx.x; e <= EL; e += kPlanThreads) excl[e] = 0;
+      if (ret_incl != nullptr)
+        for (int i = threadIdx.x; i < W * S; i += kPlanThreads) ret_incl[i] = 0;
+      if (threadIdx.x == 0 && status != nullptr) {
+        status[0] = kPlanStatusRowsExceeded;
+        status[1] = R;
+      }
+    }
+    return;
+  }
   // the cache sits behind the larger of the two scratch layouts so that both sorts can use it
   uint16_t* cache = cache_after(plan_smem, scale_map != nullptr ? W * EL : EL, cache_items);
   {
@@ -557,16 +572,11 @@ int set_smem(const void* fn, size_t bytes) {
 
 using namespace epsb;
 
-extern "C" int epsb_plan_set_max_cluster(int max_ctas) {
-  EPSB_REQUIRE(max_ctas == 1 || max_ctas == 2 || max_ctas == 4 || max_ctas == 8, EPSB_ERR_INVALID,
-               "max_ctas %d is not 1, 2, 4 or 8", max_ctas);
-  g_max_cluster.store(max_ctas, std::memory_order_relaxed);
-  return EPSB_OK;
-}
-
 extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, int E, int W, int S,
                                  int32_t* send_map, int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl,
-                                 float* zero_scale, void* stream) {
+                                 float* zero_scale, int max_cluster, void* stream) {
+  EPSB_REQUIRE(max_cluster == 0 || max_cluster == 1 || max_cluster == 2 || max_cluster == 4 || max_cluster == 8,
+               EPSB_ERR_INVALID, "max_cluster %d is not 0, 1, 2, 4 or 8", max_cluster);
   EPSB_REQUIRE(T >= 0 && k > 0 && E > 0 && W > 0 && S > 0, EPSB_ERR_INVALID, "bad sizes T=%d k=%d E=%d W=%d S=%d", T, k,
                E, W, S);
   EPSB_REQUIRE(E % W == 0, EPSB_ERR_INVALID, "num_experts %d is not divisible by ep_world_size %d", E, W);
@@ -580,7 +590,7 @@ extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T
     if (coll_incl) cudaMemsetAsync(coll_incl, 0, sizeof(int32_t) * W * S, st);
     return check_launch("source_plans(T=0)");
   }
-  const int c = cluster_size_for((int64_t)T * W);
+  const int c = cluster_size_for((int64_t)T * W, max_cluster);
   const int64_t per_cta = cta_items((int64_t)T * W, c);
   const size_t cache = key_cache_bytes(E, per_cta);
   const size_t smem = sort_smem_bytes(E) + cache;
@@ -602,8 +612,10 @@ extern "C" int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S
 extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
                                  int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map,
                                  int32_t* inv_gemm, int32_t* scale_map, int32_t* red_map, int32_t* ret_incl,
-                                 void* stream) {
+                                 int32_t* status, int max_cluster, void* stream) {
   const int EL = hi - lo;
+  EPSB_REQUIRE(max_cluster == 0 || max_cluster == 1 || max_cluster == 2 || max_cluster == 4 || max_cluster == 8,
+               EPSB_ERR_INVALID, "max_cluster %d is not 0, 1, 2, 4 or 8", max_cluster);
   EPSB_REQUIRE(EL > 0 && k > 0 && W > 0 && S > 0, EPSB_ERR_INVALID, "bad sizes EL=%d k=%d W=%d S=%d", EL, k, W, S);
   EPSB_REQUIRE(EL % S == 0, EPSB_ERR_INVALID, "Invalid num_stages: %d for local_num_experts: %d", S, EL);
   EPSB_REQUIRE((int64_t)W * EL <= kMaxBuckets, EPSB_ERR_INVALID, "W*EL = %lld exceeds %d", (long long)W * EL,
@@ -616,7 +628,7 @@ extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, 
   if (NT > 128) NT = 128;
   if (NT < 1) NT = 1;
   const int Bmax = scale_map ? W * EL : EL;
-  const int c = cluster_size_for(max_rows * k);
+  const int c = cluster_size_for(max_rows * k, max_cluster);
   const int64_t per_cta = cta_items(max_rows * k, c);
   const size_t cache = key_cache_bytes(Bmax, per_cta);
   const size_t smem = sort_smem_bytes(Bmax) + cache;
@@ -624,13 +636,13 @@ extern "C" int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, 
   if (rc) return rc;
   return launch_cluster(expert_plans_kernel, c, smem, static_cast<cudaStream_t>(stream), "expert_plans", ridx,
                         recv_incl, k, lo, hi, W, S, NT, excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl,
-                        cache ? (int)per_cta : 0);
+                        cache ? (int)per_cta : 0, (int)max_rows, status);
 }
 
 extern "C" int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W,
                                          int S, int max_tok_per_gpu, int64_t max_rows, int32_t* excl,
                                          int32_t* gemm_map, int32_t* scale_map, int32_t* red_map, int32_t* ret_incl,
-                                         void* stream) {
+                                         int32_t* status, int max_cluster, void* stream) {
   EPSB_REQUIRE(k > 0 && max_rows >= 0, EPSB_ERR_INVALID, "bad sizes k=%d max_rows=%lld", k, (long long)max_rows);
   EPSB_REQUIRE(max_rows * k <= kStaticScratchItems, EPSB_ERR_WORKSPACE,
                "max_rows * topk = %lld exceeds the built-in scratch of %lld entries; use epsb_expert_plans with a "
@@ -640,7 +652,7 @@ extern "C" int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* rec
   int rc = static_inv_gemm_scratch(&scratch);
   if (rc) return rc;
   return epsb_expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, excl, gemm_map, scratch,
-                           scale_map, red_map, ret_incl, stream);
+                           scale_map, red_map, ret_incl, status, max_cluster, stream);
 }
 
 extern "C" int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, int32_t* excl, int32_t* mapping,

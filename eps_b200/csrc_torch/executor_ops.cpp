@@ -62,10 +62,10 @@ void aok_run_fp8(fptr_t ptr, const at::Tensor& A, const at::Tensor& A_scale, con
   auto* h = reinterpret_cast<GemmHandle*>(ptr);
   TORCH_CHECK(h == nullptr || h->num_local_experts == B.size(0), "B holds ", B.size(0), " experts, executor has ",
               h ? h->num_local_experts : 0);
-  raise_if(epsb_gemm_set_sm_count(h != nullptr ? h->sm_count : 0));  // the executor's sm_count, as in the reference
   raise_if(epsb_grouped_gemm_fp8(EPSB_GEMM_PLAIN, A.data_ptr(), A_scale.data_ptr<float>(), B.data_ptr(),
                                  B_scale.data_ptr<float>(), exclusive_sum.data_ptr<int32_t>(), (int)B.size(0),
                                  max_num_tokens, B.size(1), B.size(2), C.data_ptr(), nullptr, nullptr, nullptr,
+                                 h != nullptr ? h->sm_count : 0,  // the executor's sm_count, as in the reference
                                  at::cuda::getCurrentCUDAStream().stream()));
 }
 

@@ -16,13 +16,9 @@ class AokGroupedGemm:
     def __init__(self, num_local_experts: int) -> None:
         self.num_local_experts = num_local_experts
         self.status = None
-        self._ptr = id(self)
-
-    def __del__(self) -> None:
-        self.destroy()
 
     def destroy(self) -> None:
-        self._ptr = None
+        """The reference frees its C++ object here; this object owns only tensors."""
 
     def get_workspace_size(self, cols, max_num_tokens) -> int:
         return 0  # the tile list is built inside the kernel; no workspace (reference: aok_get_workspace_size)

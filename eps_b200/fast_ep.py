@@ -30,14 +30,10 @@ class AllToAll:
         self.rows = rows
         self.send = torch.empty((rows, hidden_size), dtype=dtype, device=self.dev)
         self.recv = self.send if self.W == 1 else torch.empty((rows, hidden_size), dtype=dtype, device=self.dev)
-        self._ptr = id(self)
         self.ctx = None
 
-    def __del__(self) -> None:
-        self.destroy()
-
     def destroy(self) -> None:
-        self._ptr = None
+        """The reference frees its C++ object here; this object owns only tensors."""
 
     def dispatch(self, out_exclusive_sum: torch.Tensor, out_expert_x: torch.Tensor, dp_x: torch.Tensor,
                  indices: torch.Tensor, num_global_tokens: int) -> None:

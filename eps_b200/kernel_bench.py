@@ -112,13 +112,11 @@ def main():
         ridx = torch.randint(0, E, (R, k), dtype=torch.int32, device=dev)
         recv_incl = torch.tensor([R * (i + 1) // W for i in range(W)], dtype=torch.int32, device=dev)
         for c in (1, 8):
-            ops.plan_set_max_cluster(c)
-            ms_s = _time(lambda: ops.source_plans(idx, wts, E, W, 1), a.iters)
-            ms_e = _time(lambda: ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, 1, Tt, R), a.iters)
+            ms_s = _time(lambda: ops.source_plans(idx, wts, E, W, 1, max_cluster=c), a.iters)
+            ms_e = _time(lambda: ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, 1, Tt, R, max_cluster=c), a.iters)
             print(json.dumps({"kernel": "plans", "tokens": Tt, "experts": E, "top_k": k, "ep_world": W,
                               "received_tokens": R, "max_cluster": c, "source_plans_us": round(ms_s * 1e3, 1),
                               "expert_plans_us": round(ms_e * 1e3, 1)}))
-    ops.plan_set_max_cluster(8)
 
 
 if __name__ == "__main__":

@@ -67,6 +67,9 @@ class MoELayerFP8:
         self.kernel_launches = 0
         self.shared_sm_reserve = 4   # SMs the shared expert's GEMMs leave to the plan and gather kernels (EP=1)
         self.gateup_events = None  # optional (start, end) torch.cuda.Event pair recorded around the gate/up GEMM
+        # optional list; with ep_world_size > 1 every exchange appends (kind, start event, end event, bytes this rank
+        # sends to its peers, bytes it receives) so that a caller can report bus bandwidth
+        self.exchange_events = None
 
     def forward(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor,
                 num_global_tokens: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -88,22 +91,12 @@ class MoELayerFP8:
             side = self._comm_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                ops.gemm_set_sm_count(max(self.num_sms - self.shared_sm_reserve, 1))
-                try:
-                    shared_out = self._shared_expert(xq, xs, T)
-                finally:
-                    ops.gemm_set_sm_count(0)
+                shared_out = self._shared_expert(xq, xs, T, sm_count=max(self.num_sms - self.shared_sm_reserve, 1))
                 shared_done = torch.cuda.Event()
                 shared_done.record(side)
         # next to the shared expert's GEMMs (which occupy all but four SMs) a plan must fit into single free SMs
-        if shared_done is not None:
-            ops.plan_set_max_cluster(1)
-        try:
-            excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True,
-                                                     host_sync=self.W > 1)
-        finally:
-            if shared_done is not None:
-                ops.plan_set_max_cluster(8)   # the limit is process-wide: leave the default behind
+        excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1,
+                                                 max_cluster=1 if shared_done is not None else 0)
         n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
         rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)
         if rows_k > self.max_gemm_rows:
@@ -146,7 +139,9 @@ class MoELayerFP8:
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
                 for s in range(S):
+                    mark = self._exchange_mark("dispatch", s, comm_stream)
                     sched.dispatch(s)
+                    self._exchange_done(mark, comm_stream)
                     disp_done[s].record(comm_stream)
             for s in range(S):
                 main.wait_event(disp_done[s])
@@ -159,7 +154,9 @@ class MoELayerFP8:
                 red_done[s].record(main)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(red_done[s])
+                    mark = self._exchange_mark("combine", s, comm_stream)
                     sched.combine(s)
+                    self._exchange_done(mark, comm_stream)
                 n += 4
             all_back = torch.cuda.Event()
             all_back.record(comm_stream)
@@ -187,7 +184,7 @@ class MoELayerFP8:
                                   num_ffn_experts=router_logits.shape[1] - num_zero_experts)
         return self.forward(x, idx, w, out=out)
 
-    def _shared_expert(self, xq, xs, T):
+    def _shared_expert(self, xq, xs, T, sm_count=0):
         """The always-on expert on the quantised tokens; returns its [T, H] bf16 output (None without one)."""
         if self.shared is None or T == 0:
             return None
@@ -196,9 +193,22 @@ class MoELayerFP8:
             self._sh_excl[T] = torch.tensor([0, T], dtype=torch.int32, device=self.dev)
         sh_excl = self._sh_excl[T]
         ops.grouped_gemm_fp8(ops.GEMM_GATEUP, xq, xs, sgu, sgu_s, sh_excl, out=self.sh_act[:T],
-                             out_scales=self.sh_act_s[:T], status=self.status)
+                             out_scales=self.sh_act_s[:T], status=self.status, sm_count=sm_count)
         return ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.sh_act[:T], self.sh_act_s[:T], sd, sd_s, sh_excl,
-                                    out=self.sh_out[:T], status=self.status)
+                                    out=self.sh_out[:T], status=self.status, sm_count=sm_count)
+
+    def _exchange_mark(self, kind, stage, stream):
+        if self.exchange_events is None:
+            return None
+        out_b, in_b = self.sched.exchange_bytes(stage, combine=kind == "combine")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        return (kind, e0, e1, out_b, in_b)
+
+    def _exchange_done(self, mark, stream):
+        if mark is not None:
+            mark[2].record(stream)
+            self.exchange_events.append(mark)
 
     def _comm_stream(self):
         if getattr(self, "_cs", None) is None:
@@ -265,3 +275,37 @@ class MoELayerFP8:
         st = self.status.cpu().tolist()
         if st[0] != 0:
             raise EpsError(f"grouped GEMM gave up on a bounded wait (code {st[0]}, CTA {st[1]})")
+
+
+def synthetic_expert_codes(cfg, expert: int, device, inter: int | None = None):
+    """Random-init weights of one expert of a workloads.MoEConfig, generated (seeded by the expert id) and
+    block-quantised on `device`: (W_gate_up codes [2I,H], scales, W_down codes [H,I], scales).  expert -1 is the
+    shared expert (pass inter=cfg.shared_inter)."""
+    from . import workloads
+
+    a, b = workloads.make_expert_weights(cfg, expert, device=device, inter=inter)
+    q1, s1 = ops.quant_block128(a)
+    q2, s2 = ops.quant_block128(b)
+    return q1, s1, q2, s2
+
+
+def build_synthetic_layer(cfg, comm: Communicator | None = None, device=None, num_stages: int = 1, **kw) -> MoELayerFP8:
+    """The layer of a benchmark configuration with random-init weights of that architecture: this rank's block of
+    experts (rank * E/W ...) and the shared expert if the configuration has one."""
+    comm = comm if comm is not None else Communicator()
+    W, rank = comm.getWorldSize(), comm.getRank()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    EL = cfg.num_experts // W
+    H, I = cfg.hidden, cfg.inter
+    wgu = torch.empty((EL, 2 * I, H), dtype=torch.uint8, device=dev)
+    wgu_s = torch.empty((EL, 2 * I // 128, H // 128), dtype=torch.float32, device=dev)
+    wd = torch.empty((EL, H, I), dtype=torch.uint8, device=dev)
+    wd_s = torch.empty((EL, H // 128, I // 128), dtype=torch.float32, device=dev)
+    for le in range(EL):
+        wgu[le], wgu_s[le], wd[le], wd_s[le] = synthetic_expert_codes(cfg, rank * EL + le, dev)
+    shared = None
+    if cfg.shared_inter:
+        shared = tuple(t.unsqueeze(0) for t in synthetic_expert_codes(cfg, -1, dev, inter=cfg.shared_inter))
+    torch.cuda.synchronize(dev)
+    return MoELayerFP8(H, I, cfg.num_experts, cfg.top_k, cfg.tokens_per_rank, wgu, wgu_s, wd, wd_s, comm=comm,
+                       shared=shared, num_stages=num_stages, device=dev, **kw)

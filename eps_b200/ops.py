@@ -14,6 +14,7 @@ from ._lib import EpsError, call, ptr, stream_ptr
 
 GEMM_PLAIN, GEMM_GATEUP, GEMM_DOWN = 0, 1, 2
 ZC_MARK = 1000000
+PLAN_ROWS_EXCEEDED = 51
 INT32_MAX = 2**31 - 1
 
 
@@ -77,7 +78,7 @@ def quant_block128(w):
 # ------------------------------------------------------------------ plans
 
 
-def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True, with_bounds=False):
+def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True, with_bounds=False, max_cluster=0):
     """Source-side plans.  with_bounds=True also returns send_bounds = [0, send_incl...] (one buffer, so the
     gathers can read their [begin, end) window from the device)."""
     _check(idx, "expert_indices", torch.int32, 2)
@@ -93,7 +94,7 @@ def source_plans(idx, weights, E, W, S, want_global=True, want_zero=True, with_b
         _check(weights, "expert_scales", torch.float32, 2)
         zero_scale = torch.empty((max(T, 1),), dtype=torch.float32, device=dev)
     call("epsb_source_plans", ptr(idx), ptr(weights), T, k, E, W, S, ptr(send_map), ptr(send_incl), ptr(glob_map),
-         ptr(coll_incl), ptr(zero_scale), stream_ptr())
+         ptr(coll_incl), ptr(zero_scale), int(max_cluster), stream_ptr())
     if with_bounds:
         return send_map, send_incl, glob_map, coll_incl, zero_scale, send_bounds
     return send_map, send_incl, glob_map, coll_incl, zero_scale
@@ -109,7 +110,10 @@ def recv_plan(gathered, my_rank, W, S, total_rows=None):
     return recv_incl, remote_offset
 
 
-def expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, want_reduce=True):
+def expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, want_reduce=True, status=None,
+                 max_cluster=0):
+    """status: optional int32[2] device tensor; word 0 becomes PLAN_ROWS_EXCEEDED when the device-side row count
+    exceeds max_rows (the plans then come out empty instead of running past their buffers)."""
     _check(ridx, "recv_expert_indices", torch.int32)
     _check(recv_incl, "recv_plan", torch.int32, 1)
     dev = ridx.device
@@ -124,7 +128,8 @@ def expert_plans(ridx, recv_incl, k, lo, hi, W, S, max_tok_per_gpu, max_rows, wa
         red_map = torch.empty((n,), dtype=torch.int32, device=dev)
         ret_incl = torch.empty((W * S,), dtype=torch.int32, device=dev)
     call("epsb_expert_plans", ptr(ridx), ptr(recv_incl), k, lo, hi, W, S, max_tok_per_gpu, max_rows, ptr(excl),
-         ptr(gemm_map), ptr(inv_gemm), ptr(scale_map), ptr(red_map), ptr(ret_incl), stream_ptr())
+         ptr(gemm_map), ptr(inv_gemm), ptr(scale_map), ptr(red_map), ptr(ret_incl), ptr(status), int(max_cluster),
+         stream_ptr())
     return excl, gemm_map, inv_gemm, scale_map, red_map, ret_incl
 
 
@@ -254,11 +259,6 @@ def silu_run(gate_up, result, exclusive_sum=None, num_experts=0):
 # ------------------------------------------------------------------ grouped GEMM
 
 
-def gemm_set_sm_count(sm_count: int) -> None:
-    """SMs the persistent GEMM kernels may occupy from now on (0 = all); the sm_count of the reference's aok_create."""
-    call("epsb_gemm_set_sm_count", int(sm_count))
-
-
 def topk_sigmoid(scores, bias, num_expert_groups, topk_groups, topk, route_scale=1.0, num_ffn_experts=None,
                  expert_indices=None, expert_scales=None, score_func="sigmoid"):
     """Router (reference utils/topk_sigmoid): scores [T, E] fp32 or bf16 logits, bias [E] fp32 or None ->
@@ -299,15 +299,11 @@ def rms_norm(input, scale, eps, out=None):
     return out
 
 
-def plan_set_max_cluster(max_ctas: int) -> None:
-    """CTAs (1, 2, 4 or 8) the plan kernels may use from now on."""
-    call("epsb_plan_set_max_cluster", int(max_ctas))
-
-
 def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
-                     tile_tokens=0):
+                     tile_tokens=0, sm_count=0):
     """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.
 
+    sm_count: SMs this launch may occupy (0 = all), the sm_count of the reference's aok_create.
     tile_tokens > 0 selects the token-N kernel (weights on the MMA's M, that many tokens per tile on N);
     it exists for modes PLAIN and DOWN."""
     _check(A, "A", _FP8, 2)
@@ -331,8 +327,8 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
         c_s = None
     if tile_tokens:
         call("epsb_grouped_gemm_fp8_tn", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K,
-             ptr(C), ptr(row_w), ptr(status), int(tile_tokens), stream_ptr())
+             ptr(C), ptr(row_w), ptr(status), int(tile_tokens), int(sm_count), stream_ptr())
         return C
     call("epsb_grouped_gemm_fp8", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K, ptr(C),
-         ptr(c_s), ptr(row_w), ptr(status), stream_ptr())
+         ptr(c_s), ptr(row_w), ptr(status), int(sm_count), stream_ptr())
     return (C, c_s) if mode == GEMM_GATEUP else C

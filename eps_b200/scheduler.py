@@ -78,9 +78,8 @@ class Scheduler:
         if num_experts % self.W != 0:
             raise EpsError(f"num_experts {num_experts} is not divisible by ep_world_size {self.W}")
         self.local_num_experts = num_experts // self.W
-        if local_num_experts != self.local_num_experts:
-            # the reference passes this value on as max_num_stages (scheduler.py:37 vs scheduler_ops.cu:25,35)
-            pass
+        # local_num_experts is what the reference passes on as max_num_stages (scheduler.py:37 vs
+        # scheduler_ops.cu:25,35): an upper bound only, nothing is sized from it here
         self.lo = self.rank * self.local_num_experts
         self.hi = self.lo + self.local_num_experts
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -103,13 +102,10 @@ class Scheduler:
         else:
             self.send_scales = self.recv_scales = None
         self.context: Context | None = None
-        self._ptr = id(self)
-
-    def __del__(self) -> None:
-        self.destroy()
 
     def destroy(self) -> None:
-        self._ptr = None
+        """The reference frees its C++ object here; this object owns only tensors, which the allocator reclaims."""
+        self.context = None
 
     # ------------------------------------------------------------------ plans
 
@@ -121,17 +117,18 @@ class Scheduler:
         return Context(num_tokens, num_global_tokens, num_stages, input_quanted)
 
     def rendezvous_and_plan(self, expert_indices: torch.Tensor, expert_scales: torch.Tensor, num_global_tokens,
-                            num_stages, input_quanted, host_sync: bool = True):
+                            num_stages, input_quanted, host_sync: bool = True, max_cluster: int = 0):
         """-> (exclusive_sum [EL+1] int32 on the device, number of unique rows this rank receives).
 
         With a world of one and host_sync=False nothing is copied to the host and the second value is the
-        upper bound num_tokens (every later step reads its bounds on the device)."""
+        upper bound num_tokens (every later step reads its bounds on the device).
+        max_cluster caps the CTAs of the plan kernels (0 = up to 8)."""
         T = expert_indices.shape[0]
         ctx = self.context = self.get_context(T, num_global_tokens, num_stages, input_quanted)
         W, S, k = self.W, num_stages, self.top_k
         # --- rendezvous (reference scheduler.cu:231-283): dispatch plan, plan exchange, receive count
         (ctx.send_map, ctx.send_incl, ctx.glob_map, ctx.coll_incl, ctx.zero_scale, ctx.send_bounds) = ops.source_plans(
-            expert_indices, expert_scales, self.num_experts, W, S, with_bounds=True)
+            expert_indices, expert_scales, self.num_experts, W, S, with_bounds=True, max_cluster=max_cluster)
         if W == 1:
             ctx.recv_incl = ctx.send_incl
             if host_sync:
@@ -161,7 +158,8 @@ class Scheduler:
         self._expand_for_comm(expert_indices, self.send_idx, ctx)
         self._all2all(self.send_idx, self.recv_idx, ctx, -1, combine=False)
         (ctx.excl, ctx.gemm_map, ctx.inv_gemm, ctx.scale_map, ctx.red_map, ctx.ret_incl) = ops.expert_plans(
-            self.recv_idx, ctx.recv_incl, k, self.lo, self.hi, W, S, self.max_tok, max(rows_bound, 0))
+            self.recv_idx, ctx.recv_incl, k, self.lo, self.hi, W, S, self.max_tok, max(rows_bound, 0),
+            max_cluster=max_cluster)
         return ctx.excl, (ctx.n_recv if ctx.n_recv is not None else rows_bound)
 
     # ------------------------------------------------------------------ data path
@@ -191,6 +189,22 @@ class Scheduler:
                 sends[p].append(send[a:b])
                 recvs[p].append(recv[c:d])
         self.comm.exchange(sends, recvs)
+
+    def exchange_bytes(self, stage: int, combine: bool):
+        """(bytes this rank sends to its peers, bytes it receives from them) in the exchange of one stage, from the
+        host view of the plans; rows that stay on this rank are not counted.  A dispatched row is its FP8 (or bf16)
+        hidden row + its scales + k expert ids + k gate weights; a returned row is bf16 hidden."""
+        ctx = self.context
+        if self.W == 1 or ctx is None or ctx.host_dispatch is None:
+            return 0, 0
+        sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, self.W, ctx.num_stages, stage)
+        out_rows = sum(b - a for p, ((a, b), _) in enumerate(sl) if p != self.rank)
+        in_rows = sum(d - c for p, (_, (c, d)) in enumerate(sl) if p != self.rank)
+        if combine:
+            row = self.hidden * 2
+        else:
+            row = self.hidden * self.send_hidden.element_size() + self.scales_dim * 4 + self.top_k * 8
+        return out_rows * row, in_rows * row
 
     def prologue(self, expert_scales: torch.Tensor, hidden_states: torch.Tensor, input_scales=None,
                  recv_input_scales=None, raw_input: torch.Tensor | None = None, defer_exchange: bool = False) -> None:

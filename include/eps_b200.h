@@ -105,14 +105,14 @@ int epsb_router_topk(int score_func, const void* logits, int logits_are_bf16, co
  * -------------------------------------------------------------------------- */
 int epsb_rms_norm(void* out, const void* input, const void* scale, float eps, int64_t m, int64_t n, void* stream);
 
-/* CTAs a plan kernel may use (a thread-block cluster of 1, 2, 4 or 8; default 8, chosen per call from the item
- * count).  No counterpart in the reference, whose plan kernels are single CTAs.  Process-wide; a caller that
- * runs a plan next to a kernel occupying almost every SM sets 1, because a cluster only starts once all of its
- * CTAs fit into one GPC. */
-int epsb_plan_set_max_cluster(int max_ctas);
-
 /* ----------------------------------------------------------------------------
  * EPS scheduler plans.  All emit index layouts bit-identical to the reference.
+ *
+ * max_cluster (no counterpart in the reference, whose plan kernels are single
+ * CTAs): the plan kernels run as one thread-block cluster of 1, 2, 4 or 8 CTAs,
+ * chosen per call from the item count; max_cluster caps that (0 = up to 8).  A
+ * caller that runs a plan next to a kernel occupying almost every SM passes 1,
+ * because a cluster only starts once all of its CTAs fit into one GPC.
  * -------------------------------------------------------------------------- */
 
 /* Source-side plans, one launch.
@@ -129,7 +129,8 @@ int epsb_plan_set_max_cluster(int max_ctas);
  *      zero_scale [T] = sum of weights of the token's zero-computation slots
  * Any of glob_map/coll_incl (together) or zero_scale may be NULL to skip. */
 int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, int E, int W, int S, int32_t* send_map,
-                      int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl, float* zero_scale, void* stream);
+                      int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl, float* zero_scale, int max_cluster,
+                      void* stream);
 
 /* Receive plan from the all-gathered send plans.
  * ref: AlltoallRunner::plan -> getRecvPlan<512>
@@ -151,10 +152,18 @@ int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S, int32_t* 
  *      inv_gemm [max_rows*k]: [row*k+slot] -> GEMM row or R*k (scratch the
  *      caller provides; also useful to callers that fuse the gather)
  *      scale_map [max_rows], red_map [max_rows*k] (sentinel R*k), ret_incl [W*S]
- * scale_map/red_map/ret_incl may be NULL together to compute only the GEMM plan. */
+ * scale_map/red_map/ret_incl may be NULL together to compute only the GEMM plan.
+ * status: optional int32[2] device words.  If the row count read from recv_incl
+ *      is negative or exceeds max_rows (every buffer was sized from max_rows),
+ *      nothing is sorted: excl and ret_incl are written as all zeros (no GEMM
+ *      rows, nothing returned), status[0] = EPSB_PLAN_ROWS_EXCEEDED, status[1] =
+ *      the offending count, and the maps are left untouched.  Zero it before the
+ *      call; read it after synchronising. */
+#define EPSB_PLAN_ROWS_EXCEEDED 51
 int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
                       int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map, int32_t* inv_gemm,
-                      int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, void* stream);
+                      int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, int32_t* status, int max_cluster,
+                      void* stream);
 
 /* Same plans as epsb_expert_plans, for callers that are not allowed to allocate device memory.
  * This entry point has no counterpart in the reference.
@@ -167,16 +176,24 @@ int epsb_expert_plans(const int32_t* ridx, const int32_t* recv_incl, int k, int 
  * Here that scratch is a fixed array inside the library's device image: 2^20 int32 entries (4 MiB), held by every GPU
  * that loads the library until the process exits.  Limits and rules:
  *   - max_rows * k must be <= 1048576, otherwise EPSB_ERR_WORKSPACE is returned and nothing is launched;
- *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
- *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
- *     current) and remembers it; make that first call before any stream capture begins;
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine.  The FIRST call on a
+ *     device is still special: it looks the array's device address up (cudaGetSymbolAddress, with that device
+ *     current) and remembers it, and with CUDA's default lazy module loading that same call can be the moment the
+ *     driver loads this library's device image onto the GPU, which is when the 4 MiB are actually reserved.  So
+ *     the promise "nothing is allocated" holds from the second call on a device on: make one warm-up call per
+ *     device during set-up, before any stream capture begins;
+ *   - the remembered address belongs to the device's current primary context: after cudaDeviceReset (or any
+ *     other teardown of that context) it is stale and this entry point must not be used in the process again;
+ *   - a row count on the device that exceeds max_rows is refused like in epsb_expert_plans (status word), so the
+ *     kernel never writes past the array;
  *   - every call on a device shares the one array: two calls whose kernels overlap on the GPU (different streams)
  *     race on it.  Nothing in it has to start at zero — the kernel writes every entry it later reads — and after
  *     the call it simply holds the last call's inverse map.
  * Arguments are those of epsb_expert_plans without inv_gemm. */
 int epsb_expert_plans_noalloc(const int32_t* ridx, const int32_t* recv_incl, int k, int lo, int hi, int W, int S,
                               int max_tok_per_gpu, int64_t max_rows, int32_t* excl, int32_t* gemm_map,
-                              int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, void* stream);
+                              int32_t* scale_map, int32_t* red_map, int32_t* ret_incl, int32_t* status,
+                              int max_cluster, void* stream);
 
 /* ----------------------------------------------------------------------------
  * fast_ep plans.  ref: src/fast_ep/all_to_all/fast_ep_kernels.cu:40-176
@@ -293,19 +310,16 @@ int epsb_silu_run(const void* gate_up, void* act, const int32_t* exclusive_sum, 
  * mode EPSB_GEMM_DOWN  : C [max_rows, N] bf16 = result * row_w[m] (fp32), the
  *      top-k gate weight of GEMM row m; row_w NULL = 1.
  * -------------------------------------------------------------------------- */
-/* SMs the persistent GEMM kernels may occupy (one CTA each); 0 = all of them.
- * ref: the sm_count argument of aok_create (src/executor/aok_grouped_gemm.cu:12,34,
- * src/executor/bindings/aok_grouped_gemm_ops.cu).  Process-wide; set it before
- * the launches it should apply to (e.g. to leave SMs to a kernel running on
- * another stream). */
-int epsb_gemm_set_sm_count(int sm_count);
-
+/* sm_count: SMs this launch of the persistent kernel may occupy (one CTA each);
+ * 0 = all of them.  ref: the sm_count argument of aok_create
+ * (src/executor/aok_grouped_gemm.cu:12,34, src/executor/bindings/aok_grouped_gemm_ops.cu).
+ * A caller passes less than all to leave SMs to a kernel running on another stream. */
 #define EPSB_GEMM_PLAIN 0
 #define EPSB_GEMM_GATEUP 1
 #define EPSB_GEMM_DOWN 2
 int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
                           const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
-                          float* c_s, const float* row_w, int32_t* status, void* stream);
+                          float* c_s, const float* row_w, int32_t* status, int sm_count, void* stream);
 
 /* The same product with the operand roles swapped ("token-N"): 128 weight rows
  * are the MMA's M and an expert's tokens its N, so an expert of up to
@@ -317,7 +331,7 @@ int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void*
  * more rows take several tiles.  a_s and b_s must be 16-byte aligned. */
 int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
                              const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
-                             const float* row_w, int32_t* status, int tile_tokens, void* stream);
+                             const float* row_w, int32_t* status, int tile_tokens, int sm_count, void* stream);
 
 /* Gathers the per-GEMM-row gate weight: row_w[d] = w_recv[gemm_map[d]] for
  * d < excl[EL] (w_recv is [R,k] flat, gemm_map holds row*k+slot). */

@@ -602,6 +602,14 @@ void orc_fastep_reduce(const uint16_t* rows_bf16, const uint16_t* raw_bf16, cons
     }
 }
 
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  omp_set_num_threads(n > 0 ? n : 1);
+#else
+  (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

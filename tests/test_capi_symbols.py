@@ -37,9 +37,9 @@ def test_argument_validation_needs_no_gpu():
     with pytest.raises(EpsError, match="not divisible by group_size"):
         call("epsb_quant_1x128", None, 4, 100, None, None, 0, None)
     with pytest.raises(EpsError, match="Invalid num_stages"):
-        call("epsb_source_plans", None, None, 8, 2, 12, 2, 4, None, None, None, None, None, None)
+        call("epsb_source_plans", None, None, 8, 2, 12, 2, 4, None, None, None, None, None, 0, None)
     with pytest.raises(EpsError, match="K: 100 is not divisible by 128"):
-        call("epsb_grouped_gemm_fp8", 0, None, None, None, None, None, 4, 16, 128, 100, None, None, None, None, None)
+        call("epsb_grouped_gemm_fp8", 0, None, None, None, None, None, 4, 16, 128, 100, None, None, None, None, 0, None)
 
 
 def test_missing_library_fails_loudly(monkeypatch):

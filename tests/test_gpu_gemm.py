@@ -183,7 +183,7 @@ def test_gemm_token_n_errors(cuda):
 
 
 def test_gemm_sm_count_limit(cuda, oracle):
-    """epsb_gemm_set_sm_count (the sm_count of the reference's aok_create) changes the grid, not the result."""
+    """The sm_count argument (the sm_count of the reference's aok_create) changes the grid, not the result."""
     from eps_b200 import ops
     from eps_b200._lib import EpsError
 
@@ -192,16 +192,12 @@ def test_gemm_sm_count_limit(cuda, oracle):
     args = (_dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda), _dev(excl, cuda))
     status = torch.zeros(4, dtype=torch.int32, device=cuda)
     full = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status)
-    try:
-        ops.gemm_set_sm_count(3)
-        few = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status)
-    finally:
-        ops.gemm_set_sm_count(0)
+    few = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status, sm_count=3)
     torch.cuda.synchronize()
     _check_status(status)
     assert torch.equal(full[:D], few[:D])
     with pytest.raises(EpsError):
-        ops.gemm_set_sm_count(-1)
+        ops.grouped_gemm_fp8(ops.GEMM_PLAIN, *args, status=status, sm_count=-1)
 
 
 def test_gemm_errors(cuda):

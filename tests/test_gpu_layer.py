@@ -86,6 +86,43 @@ def test_layer_vs_oracle(cuda, oracle, case):
     assert ok, msg
 
 
+@pytest.mark.parametrize("cfg_id", [0, 1, 2, 3, 4])
+def test_layer_full_size_sampled(cuda, oracle, cfg_id):
+    """Every benchmark configuration at its real hidden / intermediate / expert / top-k / token sizes on one GPU
+    (all experts resident; config 4 with its 256 identity experts, config 2 with the Zipf router bias), checked on
+    a seeded sample of 64 tokens against the fp32 oracle evaluated on those tokens only.  The weights are
+    regenerated per expert from their seeds for the oracle, so only the experts the sample hits are ever on the host."""
+    from eps_b200 import workloads
+    from eps_b200.layer import build_synthetic_layer, synthetic_expert_codes
+    from oracle import layer_check
+
+    cfg = workloads.CONFIGS[cfg_id]
+    layer = build_synthetic_layer(cfg, device=cuda)
+    x = workloads.make_tokens(cfg)
+    idx, w = workloads.make_routing(cfg)
+    out = layer.forward(x.to(cuda), idx.to(cuda), w.to(cuda))
+    torch.cuda.synchronize()
+    layer.check_status()
+    sample = layer_check.sample_tokens(cfg.tokens_per_rank, 64, seed=100 + cfg_id)
+
+    def expert_weights(e):
+        return tuple(t.cpu().numpy() for t in synthetic_expert_codes(cfg, e, cuda))
+
+    shared = None
+    if cfg.shared_inter:
+        shared = tuple(t.cpu().numpy()[None] for t in synthetic_expert_codes(cfg, -1, cuda, inter=cfg.shared_inter))
+    res = layer_check.check_rows(_bits(x)[sample], idx.numpy()[sample], w.numpy()[sample],
+                                 out[torch.from_numpy(sample).to(cuda)].float().cpu().numpy(), expert_weights,
+                                 shared=shared)
+    print(f"cfg{cfg_id}: {res}")
+    assert res["checked_tokens"] == 64
+    assert res["ok"], res
+    # the tolerance as stated (no bf16-rounding term) is reported beside it; it holds too on these outputs
+    assert res["worst_ratio"] <= 1.0, res
+    del layer
+    torch.cuda.empty_cache()
+
+
 def test_scheduler_reference_flow_bf16(cuda, oracle):
     """Drives Scheduler exactly like a caller of the reference (bf16 rows, reference arithmetic) with the
     expert FFN replaced by the identity: output[t] = sum_j w[t,j] * x[t] over FFN slots + identity-expert term."""

@@ -87,17 +87,13 @@ def test_plans_same_for_every_cluster_size(cuda):
     E, k, T, W, S = 64, 6, 3000, 2, 2
     idx, w = random_routing(rng, T, k, E, 3)
     outs = []
-    try:
-        for c in (1, 2, 4, 8):
-            ops.plan_set_max_cluster(c)
-            src = ops.source_plans(_dev(idx, cuda), _dev(w, cuda), E, W, S)
-            recv_incl = torch.tensor([T // 2, T, T, T], dtype=torch.int32, device=cuda)  # two sources, two stages
-            ridx = _dev(np.where(idx < 0, -1, idx).astype(np.int32), cuda)
-            exp = ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, S, T, T)
-            torch.cuda.synchronize()
-            outs.append([t.cpu().numpy().copy() for t in list(src[:4]) + list(exp)])
-    finally:
-        ops.plan_set_max_cluster(8)
+    for c in (1, 2, 4, 8):
+        src = ops.source_plans(_dev(idx, cuda), _dev(w, cuda), E, W, S, max_cluster=c)
+        recv_incl = torch.tensor([T // 2, T, T, T], dtype=torch.int32, device=cuda)  # two sources, two stages
+        ridx = _dev(np.where(idx < 0, -1, idx).astype(np.int32), cuda)
+        exp = ops.expert_plans(ridx, recv_incl, k, 0, E // W, W, S, T, T, max_cluster=c)
+        torch.cuda.synchronize()
+        outs.append([t.cpu().numpy().copy() for t in list(src[:4]) + list(exp)])
     n_sent = int(outs[0][1][-1])
     D = int(outs[0][4][-1])
     n_red = int(outs[0][9][-1])
@@ -110,7 +106,39 @@ def test_plans_same_for_every_cluster_size(cuda):
         assert np.array_equal(o[8][:n_red * k], outs[0][8][:n_red * k])
         assert np.array_equal(o[9], outs[0][9])
     with pytest.raises(Exception):
-        ops.plan_set_max_cluster(3)
+        ops.source_plans(_dev(idx, cuda), _dev(w, cuda), E, W, S, max_cluster=3)
+
+
+def test_expert_plans_refuse_more_rows_than_promised(cuda):
+    """A receive plan that claims more rows than max_rows (what every buffer was sized from) is not followed:
+    the kernel compares and returns, the plans come out empty, the status word names the count, and the maps
+    stay as they were."""
+    from eps_b200 import ops
+
+    k, EL, W, S, max_rows = 4, 8, 1, 1, 64
+    ridx = torch.randint(0, EL, (max_rows, k), dtype=torch.int32, device=cuda)
+    for claimed in (max_rows + 1, 5 * max_rows, -3):
+        recv_incl = torch.tensor([claimed], dtype=torch.int32, device=cuda)
+        status = torch.zeros(2, dtype=torch.int32, device=cuda)
+        n = max_rows * k
+        excl = torch.full((EL + 1,), 7, dtype=torch.int32, device=cuda)
+        gemm_map, inv_gemm, red_map = (torch.full((n,), -9, dtype=torch.int32, device=cuda) for _ in range(3))
+        scale_map = torch.full((max_rows,), -9, dtype=torch.int32, device=cuda)
+        ret_incl = torch.full((W * S,), 7, dtype=torch.int32, device=cuda)
+        from eps_b200._lib import call, ptr, stream_ptr
+        call("epsb_expert_plans", ptr(ridx), ptr(recv_incl), k, 0, EL, W, S, max_rows, max_rows, ptr(excl),
+             ptr(gemm_map), ptr(inv_gemm), ptr(scale_map), ptr(red_map), ptr(ret_incl), ptr(status), 0, stream_ptr())
+        torch.cuda.synchronize()
+        assert status.tolist() == [ops.PLAN_ROWS_EXCEEDED, claimed]
+        assert excl.tolist() == [0] * (EL + 1) and ret_incl.tolist() == [0]
+        for t in (gemm_map, inv_gemm, red_map, scale_map):
+            assert bool((t == -9).all())
+    # a count within the promise leaves the status word alone
+    status = torch.zeros(2, dtype=torch.int32, device=cuda)
+    recv_incl = torch.tensor([max_rows], dtype=torch.int32, device=cuda)
+    out = ops.expert_plans(ridx, recv_incl, k, 0, EL, W, S, max_rows, max_rows, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0] and int(out[0][-1]) == max_rows * k
 
 
 def test_source_plans_empty_tokens(cuda):

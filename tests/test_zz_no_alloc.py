@@ -43,9 +43,9 @@ def _plans_both_ways(cuda, oracle, seed, W, S, E, k, T, max_tok):
         a, b = outputs(), outputs()
         inv = torch.empty((max_rows * k,), dtype=torch.int32, device=cuda)
         call("epsb_expert_plans", ptr(ridx), ptr(recv_incl), k, r * EL, (r + 1) * EL, W, S, max_tok, max_rows,
-             ptr(a[0]), ptr(a[1]), ptr(inv), ptr(a[2]), ptr(a[3]), ptr(a[4]), stream_ptr())
+             ptr(a[0]), ptr(a[1]), ptr(inv), ptr(a[2]), ptr(a[3]), ptr(a[4]), None, 0, stream_ptr())
         call("epsb_expert_plans_noalloc", ptr(ridx), ptr(recv_incl), k, r * EL, (r + 1) * EL, W, S, max_tok,
-             max_rows, ptr(b[0]), ptr(b[1]), ptr(b[2]), ptr(b[3]), ptr(b[4]), stream_ptr())
+             max_rows, ptr(b[0]), ptr(b[1]), ptr(b[2]), ptr(b[3]), ptr(b[4]), None, 0, stream_ptr())
         torch.cuda.synchronize()
         D = int(rk["excl"][-1])
         for x, y in zip(a, b):
@@ -67,4 +67,4 @@ def test_noalloc_rejects_sizes_beyond_the_built_in_scratch(cuda):
 
     with pytest.raises(EpsError, match="exceeds the built-in scratch"):
         call("epsb_expert_plans_noalloc", None, None, 8, 0, 8, 1, 1, 4096, (1 << 20) // 8 + 1, None, None, None, None,
-             None, None)
+             None, None, 0, None)
