@@ -174,9 +174,9 @@ class CpuLayerSample:
 
 def cpu_sample_experts(cfg, per_pass_budget_s=3.0):
     """Experts in the CPU sample: about `per_pass_budget_s` of work on this host.  One expert row costs
-    6*H*I flops; the scalar-blocked oracle sustains roughly 1.3 GFLOP/s per core."""
+    6*H*I flops; the blocked oracle sustains roughly 10 GFLOP/s per core."""
     rows_per_expert = cfg.tokens_per_rank * cfg.top_k / max(cfg.num_experts + cfg.num_zero_experts, 1)
-    sec_per_expert = rows_per_expert * 6.0 * cfg.hidden * cfg.inter / (1.3e9 * host_cores()) + 0.02
+    sec_per_expert = rows_per_expert * 6.0 * cfg.hidden * cfg.inter / (10e9 * host_cores()) + 0.02
     return int(max(1, min(cfg.num_experts // 4, per_pass_budget_s / sec_per_expert)))
 
 
@@ -200,7 +200,7 @@ def run_reference(args, cfg, rank):
 
     cores = orc.set_num_threads(host_cores())
     # keep warm-up + steps within about two minutes whatever K is
-    budget = max(0.5, min(3.0, 100.0 / max(args.steps + args.warmup, 1)))
+    budget = max(0.5, min(4.0, 100.0 / max(args.steps + args.warmup, 1)))
     sample = CpuLayerSample(cfg, cpu_sample_experts(cfg, budget))
     for _ in range(args.warmup):
         sample.run()

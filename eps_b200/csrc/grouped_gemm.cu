@@ -411,11 +411,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
         if (good) tc_fence_after();
         return good;
       };
-      // Drain of one K step: two tcgen05.ld of 32 columns are issued together and awaited once (two
-      // waits per K step, 64 temporaries beside the 128 accumulators: no spills at 232 registers).  Measured
-      // on B200 the K-step period is set by the MMA <-> epilogue hand-off latency over the two TMEM buffers
-      // (~0.7 us), not by these loads, the scale loads or the fold; deeper register pipelines only spilled.
+      // Drain of a K step, software-pipelined: the thread's 128 columns leave TMEM as four loads of 32 columns,
+      // and the load of chunk c+1 is issued BEFORE the fold of chunk c, so that TMEM reads and FMAs of one warp
+      // overlap (tcgen05.wait::ld waits for every load the thread has in flight, hence exactly one is kept in
+      // flight).  The chain crosses K steps: once the fourth load of a step has landed the buffer is released to
+      // the MMA warp, the first load of the NEXT step is issued, and only then is the fourth chunk folded.
+      // Two 32-register landing arrays beside the 128 accumulators: no spills at 232 registers.
       uint32_t t0[32], t1[32];
+      ok = wait_full(it);
+      if (!ok) break;
+      tmem_ld32_async(tmem_of(it) + col_of(0), t0);
       for (int kb = 0; kb < KB; kb++, it++) {
         s0 = sa * sb0;
         s1 = sa * sb1;
@@ -424,27 +429,29 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
           sb0 = __ldg(bs0 + kb + 1);
           sb1 = __ldg(bs1 + kb + 1);
         }
-        ok = wait_full(it);
-        if (!ok) break;
+        const float sc = kMode == EPSB_GEMM_GATEUP ? s1 : s0;
         const uint32_t tb = tmem_of(it);
-        tmem_ld32_async(tb + col_of(0), t0);
-        tmem_ld32_async(tb + col_of(1), t1);
         tmem_wait(t0);
-        tmem_tie(t1);
+        tmem_ld32_async(tb + col_of(1), t1);
 #pragma unroll
         for (int i = 0; i < 32; i++) acc[i] = fmaf(__uint_as_float(t0[i]), s0, acc[i]);
+        tmem_wait(t1);
+        tmem_ld32_async(tb + col_of(2), t0);
 #pragma unroll
         for (int i = 0; i < 32; i++) acc[32 + i] = fmaf(__uint_as_float(t1[i]), s0, acc[32 + i]);
-        tmem_ld32_async(tb + col_of(2), t0);
-        tmem_ld32_async(tb + col_of(3), t1);
         tmem_wait(t0);
-        tmem_tie(t1);
+        tmem_ld32_async(tb + col_of(3), t1);
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[64 + i] = fmaf(__uint_as_float(t0[i]), sc, acc[64 + i]);
+        tmem_wait(t1);   // every load of this K step has landed: the buffer may be overwritten
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm->tmem_empty[it & 1u]);
-        const float sc = kMode == EPSB_GEMM_GATEUP ? s1 : s0;
-#pragma unroll
-        for (int i = 0; i < 32; i++) acc[64 + i] = fmaf(__uint_as_float(t0[i]), sc, acc[64 + i]);
+        if (kb + 1 < KB) {
+          ok = wait_full(it + 1);
+          if (!ok) break;
+          tmem_ld32_async(tmem_of(it + 1) + col_of(0), t0);
+        }
 #pragma unroll
         for (int i = 0; i < 32; i++) acc[96 + i] = fmaf(__uint_as_float(t1[i]), sc, acc[96 + i]);
       }
