@@ -238,6 +238,9 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="repeat the timed block of --steps steps until this much time has been timed")
     ap.add_argument("--parity-tokens", type=int, default=64, help="output rows per rank checked against the oracle")
+    ap.add_argument("--transport", default="auto", choices=["auto", "ipc", "nccl"],
+                    help="expert-parallel transport at N > 1: this library's peer-store kernels (ipc, the default) "
+                         "or grouped NCCL send/recv")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -267,7 +270,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-        comm = Communicator(None, CommunicatorParams(rank, world, world))
+        comm = Communicator(None, CommunicatorParams(rank, world, world), transport=args.transport)
     else:
         comm = Communicator(None, CommunicatorParams(0, 1, 1))
     if cfg.num_experts % world:
@@ -444,17 +447,21 @@ def main():
     if ev and roofline is not None:
         bus = {}
         for kind in ("dispatch", "combine"):
-            rows = [(a.elapsed_time(b), o, i_) for k_, a, b, o, i_ in ev if k_ == kind]
+            rows = [a.elapsed_time(b) for k_, a, b, st_ in ev if k_ == kind]
             if rows:
-                ms = statistics.median(r[0] for r in rows)
-                byt = statistics.median(max(r[1], r[2]) for r in rows)
-                bus[kind] = {"ms": ms, "bytes": int(byt), "gbs": byt / (ms * 1e-3) / 1e9}
+                ms = statistics.median(rows)
+                # the routing is the same in every step: bytes of the last call's plans, all stages
+                byt = max(layer.sched.exchange_bytes(-1, combine=kind == "combine"))
+                bus[kind] = {"ms": ms * stages, "bytes": int(byt), "gbs": byt / (ms * stages * 1e-3) / 1e9}
         if bus:
             t = torch.tensor([bus.get("dispatch", {}).get("gbs", 0.0), bus.get("combine", {}).get("gbs", 0.0)],
                              dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)
             roofline["bus_gbs"] = {"dispatch": float(t[0].item()), "combine": float(t[1].item()), "peak": 900.0,
-                                   "rank0": bus, "note": "min over ranks of max(bytes out, bytes in) / event time"}
+                                   "rank0": bus, "note": "min over ranks of max(bytes out, bytes in) / CUDA-event time of the exchange on its stream"
+                                           "; with the device-side transport the dispatch time covers plan exchange + "
+                                           "permute-on-send + flag wait, the combine time the fused local reduce + store",
+                                   "transport": comm.transport}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:

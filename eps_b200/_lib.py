@@ -45,6 +45,20 @@ SIGNATURES = {
     "epsb_router_topk_sigmoid": [_P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_gather_row_weights": [_P, _P, _P, _I, _L, _P, _P],
+    "epsb_symm_alloc": [_L, _P, _P],
+    "epsb_symm_open": [_P, _P],
+    "epsb_symm_close": [_P],
+    "epsb_symm_free": [_P],
+    "epsb_exchange_region_bytes": [_I, _I, _I, _I, _L, _I, _I, _P],
+    "epsb_exchange_create": [_I, _I, _I, _I, _I, _L, _I, _I, _P, _P],
+    "epsb_exchange_destroy": [_P],
+    "epsb_exchange_begin": [_P, _P],
+    "epsb_exchange_arena": [_P, _I, _I, _P],
+    "epsb_exchange_publish_plans": [_P, _P, _P, _I, _P],
+    "epsb_exchange_recv_plans": [_P, _I, _P, _P, _L, _P],
+    "epsb_exchange_put": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "epsb_exchange_wait": [_P, _I, _P, _L, _P],
+    "epsb_exchange_local_reduce_put": [_P, _I, _P, _P, _P, _I, _I, _L, _P],
 }
 
 _lib = None

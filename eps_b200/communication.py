@@ -3,15 +3,23 @@
 Mirrors the surface of the reference's MscclppCommunicator (python/eps/communication/__init__.py:35-71,
 src/communication/msccl_comm.cuh:14): create from a unique id + (rank, world, ranks_per_node), barrier,
 rank/world queries.  The reference moves bytes with mscclpp SM-copy kernels over CUDA-IPC arenas; here
-the variable-size all-to-all is one grouped NCCL send/recv per call over NVLink/NVSwitch (gloo on CPU for
-tests), launched through torch.distributed.  A world of one never touches a process group.
+two transports exist.  "ipc" (the default on GPUs): every rank's receive arenas live in a symmetric region that
+all ranks of the box map through CUDA IPC, and the exchange is done by this library's own kernels storing rows
+straight into the destination's arena (see Scheduler and include/eps_b200.h, "Expert-parallel exchange over peer
+memory"); torch.distributed only carries the 64-byte memory handles at set-up.  "nccl": the variable-size
+all-to-all is one grouped NCCL send/recv per call (gloo on CPU for tests), launched through torch.distributed,
+with one host read of the exchanged plans per call.  A world of one never touches a process group.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 
+import ctypes
+
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 @dataclass
@@ -24,7 +32,7 @@ class CommunicatorParams:
 class Communicator:
     """One expert-parallel group.  `group` is a torch.distributed process group (None = default group)."""
 
-    def __init__(self, unique_id=None, p: CommunicatorParams | None = None, group=None):
+    def __init__(self, unique_id=None, p: CommunicatorParams | None = None, group=None, transport: str = "auto"):
         if p is None:
             if dist.is_available() and dist.is_initialized():
                 p = CommunicatorParams(dist.get_rank(group), dist.get_world_size(group), dist.get_world_size(group))
@@ -41,6 +49,13 @@ class Communicator:
                 raise RuntimeError("rank/world of the process group do not match the communicator parameters")
             if self.world != self.num_ranks_per_node:
                 raise RuntimeError("multi-node expert parallelism is not supported: one NVSwitch box only")
+        if transport not in ("auto", "ipc", "nccl"):
+            raise RuntimeError(f"transport must be 'auto', 'ipc' or 'nccl', got {transport!r}")
+        if transport == "auto":
+            on_gpu = self.world > 1 and dist.get_backend(group) == "nccl"
+            transport = "ipc" if on_gpu and self.world <= 8 else "nccl"
+        self.transport = transport
+        self._regions = []   # (local pointer, [mapped peer pointers]) of every symmetric allocation
 
     # reference API names
     @staticmethod
@@ -60,6 +75,47 @@ class Communicator:
     def barrier(self) -> None:
         if self.world > 1:
             dist.barrier(group=self.group)
+
+    # ---- symmetric memory (transport "ipc")
+
+    def symm_alloc(self, nbytes: int):
+        """Collective.  Allocates `nbytes` of zeroed device memory on every rank and maps every rank's block into
+        every process: -> (this rank's pointer, [pointer of rank r's block in this process for r in range(world)])."""
+        local = ctypes.c_void_p()
+        handle = (ctypes.c_uint8 * 64)()
+        _lib.call("epsb_symm_alloc", int(nbytes), ctypes.byref(local), handle)
+        peers = [local.value] * self.world
+        if self.world > 1:
+            dev = torch.device("cuda", torch.cuda.current_device())
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
+            allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh.view(-1), mine, group=self.group)
+            allh = allh.cpu()
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                h = (ctypes.c_uint8 * 64)(*allh[r].tolist())
+                p = ctypes.c_void_p()
+                _lib.call("epsb_symm_open", h, ctypes.byref(p))
+                peers[r] = p.value
+            dist.barrier(group=self.group)
+        self._regions.append((local.value, peers))
+        return local.value, peers
+
+    def symm_free(self, local_ptr: int) -> None:
+        """Collective.  Unmaps the peers' blocks and frees this rank's; no rank may still be writing to it."""
+        for i, (loc, peers) in enumerate(self._regions):
+            if loc == local_ptr:
+                if self.world > 1:
+                    torch.cuda.synchronize()
+                    dist.barrier(group=self.group)
+                    for r, p in enumerate(peers):
+                        if r != self.rank:
+                            _lib.call("epsb_symm_close", p)
+                    dist.barrier(group=self.group)
+                _lib.call("epsb_symm_free", loc)
+                del self._regions[i]
+                return
 
     # ---- collectives used by the plans
 

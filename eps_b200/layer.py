@@ -67,8 +67,8 @@ class MoELayerFP8:
         self.kernel_launches = 0
         self.shared_sm_reserve = 4   # SMs the shared expert's GEMMs leave to the plan and gather kernels (EP=1)
         self.gateup_events = None  # optional (start, end) torch.cuda.Event pair recorded around the gate/up GEMM
-        # optional list; with ep_world_size > 1 every exchange appends (kind, start event, end event, bytes this rank
-        # sends to its peers, bytes it receives) so that a caller can report bus bandwidth
+        # optional list; with ep_world_size > 1 every exchange appends (kind, start event, end event, stage) so that a
+        # caller can report bus bandwidth (bytes per exchange: Scheduler.exchange_bytes, after the timed region)
         self.exchange_events = None
 
     def forward(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor,
@@ -95,15 +95,24 @@ class MoELayerFP8:
                 shared_done = torch.cuda.Event()
                 shared_done.record(side)
         # next to the shared expert's GEMMs (which occupy all but four SMs) a plan must fit into single free SMs
+        # device-side exchange with one stage: the FP8 rows and their scales travel with the expert ids
+        eager = sched.peer is not None and S == 1
+        mark = self._exchange_mark("dispatch", 0, torch.cuda.current_stream()) if eager else None
         excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1,
-                                                 max_cluster=1 if shared_done is not None else 0)
-        n += 3 + (1 if self.W > 1 else 0)  # source plans, index gather, expert plans (+ receive plan)
+                                                 max_cluster=1 if shared_done is not None else 0,
+                                                 payload=(xq, xs) if eager else None)
+        self._exchange_done(mark, torch.cuda.current_stream())
+        # source plans, expert plans + (NCCL transport: index gather, receive plan | device-side exchange: publish,
+        # receive plans, put, wait) or the index gather of a world of one
+        n += 2 + (4 if sched.peer is not None else (2 if self.W > 1 else 1))
         rows_k = max(sched.context.rows_bound, 0) * min(self.k, EL)
         if rows_k > self.max_gemm_rows:
             raise EpsError(f"{rows_k} possible GEMM rows exceed max_gemm_rows {self.max_gemm_rows}")
         D = max(rows_k, 1)
         sched.prologue(expert_weights, xq, xs, self.A_s[:D], raw_input=x, defer_exchange=True)
-        n += 5  # gate weights, hidden rows, scales to send order; scales to GEMM order; GEMM-row gate weights
+        # NCCL transport / world of one: gate weights, hidden rows, scales to send order; scales to GEMM order;
+        # GEMM-row gate weights.  Device-side exchange: nothing is staged, only the GEMM-row gate weights.
+        n += 1 if sched.peer is not None else 5
         row_w = sched.gemm_row_weights() if self.W == 1 else None
         eps_ = EL // S
 
@@ -139,7 +148,7 @@ class MoELayerFP8:
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
                 for s in range(S):
-                    mark = self._exchange_mark("dispatch", s, comm_stream)
+                    mark = None if eager else self._exchange_mark("dispatch", s, comm_stream)
                     sched.dispatch(s)
                     self._exchange_done(mark, comm_stream)
                     disp_done[s].record(comm_stream)
@@ -150,14 +159,16 @@ class MoELayerFP8:
                     row_w = sched.gemm_row_weights()
                 sched.gemm_expand(self.A[:D], s)
                 stage_gemms(s)
-                sched.local_reduce(self.Y[:D], s, pre_weighted=True)
+                mark_lr = self._exchange_mark("combine", s, main) if sched.peer is not None else None
+                sched.local_reduce(self.Y[:D], s, pre_weighted=True)   # device-side exchange: reduce + store at the source
+                self._exchange_done(mark_lr, main)
                 red_done[s].record(main)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(red_done[s])
-                    mark = self._exchange_mark("combine", s, comm_stream)
+                    mark = self._exchange_mark("combine", s, comm_stream) if sched.peer is None else None
                     sched.combine(s)
                     self._exchange_done(mark, comm_stream)
-                n += 4
+                n += 5 if sched.peer is not None else 4
             all_back = torch.cuda.Event()
             all_back.record(comm_stream)
         shared_out = self._shared_expert(xq, xs, T) if self.W > 1 else shared_out
@@ -200,10 +211,9 @@ class MoELayerFP8:
     def _exchange_mark(self, kind, stage, stream):
         if self.exchange_events is None:
             return None
-        out_b, in_b = self.sched.exchange_bytes(stage, combine=kind == "combine")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        return (kind, e0, e1, out_b, in_b)
+        return (kind, e0, e1, stage)
 
     def _exchange_done(self, mark, stream):
         if mark is not None:
@@ -271,7 +281,9 @@ class MoELayerFP8:
         hp["d2h"].synchronize()
 
     def check_status(self) -> None:
-        """Raises if a bounded device-side wait of a GEMM kernel expired (synchronises)."""
+        """Raises if a bounded device-side wait of a GEMM kernel or of the exchange expired (synchronises)."""
+        if self.sched.peer is not None:
+            self.sched.peer.check_status()
         st = self.status.cpu().tolist()
         if st[0] != 0:
             raise EpsError(f"grouped GEMM gave up on a bounded wait (code {st[0]}, CTA {st[1]})")

@@ -10,12 +10,115 @@ path uses the slots the reference already has: `input_quanted`, `input_scales`, 
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import torch
 
-from . import ops
+from . import _lib, ops
 from ._lib import EpsError
 from .communication import Communicator
+
+ARENA_IDX, ARENA_WEIGHTS, ARENA_HIDDEN, ARENA_SCALES, ARENA_OUT, ARENA_RECV_PLAN = range(6)
+PUT_META, PUT_SCALES, PUT_HIDDEN = 1, 2, 4
+FLAG_META = 1
+
+
+class _RawDeviceMemory:
+    """Lets torch view device memory this package allocated itself (zero-copy, not owning)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def device_view(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+    flat = torch.as_tensor(_RawDeviceMemory(ptr, max(n, 1)), device=device)
+    return flat[:n].view(dtype).view(*shape)
+
+
+class PeerExchange:
+    """This rank's end of the device-side exchange (include/eps_b200.h, "Expert-parallel exchange over peer
+    memory"): the symmetric region, the C handle and torch views of the receive arenas."""
+
+    def __init__(self, comm: Communicator, max_tok: int, S_max: int, k: int, H: int, hidden_elem: int,
+                 scales_dim: int, device):
+        self.comm, self.S_max = comm, S_max
+        W = comm.getWorldSize()
+        nbytes = ctypes.c_int64()
+        _lib.call("epsb_exchange_region_bytes", W, max_tok, S_max, k, H, hidden_elem, scales_dim, ctypes.byref(nbytes))
+        self.local, peers = comm.symm_alloc(nbytes.value)
+        arr = (ctypes.c_void_p * W)(*peers)
+        h = ctypes.c_void_p()
+        _lib.call("epsb_exchange_create", comm.getRank(), W, max_tok, S_max, k, H, hidden_elem, scales_dim, arr,
+                  ctypes.byref(h))
+        self.handle = h
+        self.epoch = 0
+        rows = max(max_tok, 1) * W
+        hid_dt = torch.uint8 if hidden_elem == 1 else torch.bfloat16
+
+        def arena(which, par, shape, dtype):
+            p = ctypes.c_void_p()
+            _lib.call("epsb_exchange_arena", self.handle, which, par, ctypes.byref(p))
+            return device_view(p.value, shape, dtype, device)
+
+        self.recv_idx = [arena(ARENA_IDX, par, (rows, k), torch.int32) for par in (0, 1)]
+        self.recv_w = [arena(ARENA_WEIGHTS, par, (rows, k), torch.float32) for par in (0, 1)]
+        self.recv_hidden = [arena(ARENA_HIDDEN, par, (rows, H), hid_dt) for par in (0, 1)]
+        self.recv_scales = ([arena(ARENA_SCALES, par, (rows, scales_dim), torch.float32) for par in (0, 1)]
+                            if scales_dim > 0 else [None, None])
+        self.recv_out = arena(ARENA_OUT, 0, (rows, H), torch.bfloat16)
+        self.recv_plan = arena(ARENA_RECV_PLAN, 0, (W * S_max,), torch.int32)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.timeout_ns = 0   # 0 = the library's default (2 s)
+
+    def begin(self) -> int:
+        e = ctypes.c_int()
+        _lib.call("epsb_exchange_begin", self.handle, ctypes.byref(e))
+        self.epoch = e.value
+        return self.epoch
+
+    @property
+    def par(self) -> int:
+        return self.epoch & 1
+
+    def flag_dispatch(self, stage: int) -> int:
+        return 2 + max(stage, 0)
+
+    def flag_combine(self, stage: int) -> int:
+        return 2 + self.S_max + max(stage, 0)
+
+    def publish_plans(self, send_incl, coll_incl, S):
+        _lib.call("epsb_exchange_publish_plans", self.handle, _lib.ptr(send_incl), _lib.ptr(coll_incl), S,
+                  _lib.stream_ptr())
+
+    def recv_plans(self, S, recv_incl):
+        _lib.call("epsb_exchange_recv_plans", self.handle, S, _lib.ptr(recv_incl), _lib.ptr(self.status),
+                  self.timeout_ns, _lib.stream_ptr())
+
+    def put(self, flag_slot, stage, mask, idx, w, hidden, scales, send_map, send_incl, T, S):
+        _lib.call("epsb_exchange_put", self.handle, flag_slot, stage, mask, _lib.ptr(idx), _lib.ptr(w),
+                  _lib.ptr(hidden), _lib.ptr(scales), _lib.ptr(send_map), _lib.ptr(send_incl), T, S,
+                  _lib.stream_ptr())
+
+    def wait(self, flag_slot):
+        _lib.call("epsb_exchange_wait", self.handle, flag_slot, _lib.ptr(self.status), self.timeout_ns,
+                  _lib.stream_ptr())
+
+    def local_reduce_put(self, flag_slot, y, red_map, ret_incl, S, stage, max_rows):
+        _lib.call("epsb_exchange_local_reduce_put", self.handle, flag_slot, _lib.ptr(y), _lib.ptr(red_map),
+                  _lib.ptr(ret_incl), S, stage, max_rows, _lib.stream_ptr())
+
+    def check_status(self) -> None:
+        st = self.status.cpu().tolist()
+        if st[0] != 0:
+            raise EpsError(f"expert-parallel exchange failed (code {st[0]}, peer {st[1]})")
+
+    def destroy(self) -> None:
+        if self.handle is not None:
+            self.comm.symm_free(self.local)
+            _lib.call("epsb_exchange_destroy", self.handle)
+            self.handle = None
 
 
 class Context:
@@ -93,19 +196,37 @@ class Scheduler:
             s = torch.empty((rows, cols), dtype=dtype, device=dev)
             return s, (s if self.W == 1 else torch.empty((rows, cols), dtype=dtype, device=dev))
 
-        self.send_idx, self.recv_idx = pair(top_k, torch.int32)
-        self.send_w, self.recv_w = pair(top_k, torch.float32)
-        self.send_hidden, self.recv_hidden = pair(hidden_size, in_dt)
-        self.send_out, self.recv_out = pair(hidden_size, torch.bfloat16)
-        if input_scales_dim > 0:
-            self.send_scales, self.recv_scales = pair(input_scales_dim, torch.float32)
+        self.peer = None
+        self.hidden_dtype = in_dt
+        if self.W > 1 and self.comm.transport == "ipc":
+            # device-side exchange: the receive arenas live in the symmetric region, nothing is staged for sending
+            self.peer = PeerExchange(self.comm, self.max_tok, self.local_num_experts, top_k, hidden_size,
+                                     torch.empty((), dtype=in_dt).element_size(), input_scales_dim, dev)
+            self.recv_out = self.peer.recv_out
+            self._select_arenas()
         else:
-            self.send_scales = self.recv_scales = None
+            self.send_idx, self.recv_idx = pair(top_k, torch.int32)
+            self.send_w, self.recv_w = pair(top_k, torch.float32)
+            self.send_hidden, self.recv_hidden = pair(hidden_size, in_dt)
+            self.send_out, self.recv_out = pair(hidden_size, torch.bfloat16)
+            if input_scales_dim > 0:
+                self.send_scales, self.recv_scales = pair(input_scales_dim, torch.float32)
+            else:
+                self.send_scales = self.recv_scales = None
         self.context: Context | None = None
 
+    def _select_arenas(self) -> None:
+        """The dispatch arenas of the current call (they alternate with the exchange's epoch)."""
+        pe, par = self.peer, self.peer.par
+        self.recv_idx, self.recv_w = pe.recv_idx[par], pe.recv_w[par]
+        self.recv_hidden, self.recv_scales = pe.recv_hidden[par], pe.recv_scales[par]
+
     def destroy(self) -> None:
-        """The reference frees its C++ object here; this object owns only tensors, which the allocator reclaims."""
+        """Collective when the device-side exchange is in use (the symmetric region is unmapped everywhere)."""
         self.context = None
+        if self.peer is not None:
+            self.peer.destroy()
+            self.peer = None
 
     # ------------------------------------------------------------------ plans
 
@@ -117,12 +238,16 @@ class Scheduler:
         return Context(num_tokens, num_global_tokens, num_stages, input_quanted)
 
     def rendezvous_and_plan(self, expert_indices: torch.Tensor, expert_scales: torch.Tensor, num_global_tokens,
-                            num_stages, input_quanted, host_sync: bool = True, max_cluster: int = 0):
+                            num_stages, input_quanted, host_sync: bool = True, max_cluster: int = 0,
+                            payload=None):
         """-> (exclusive_sum [EL+1] int32 on the device, number of unique rows this rank receives).
 
         With a world of one and host_sync=False nothing is copied to the host and the second value is the
         upper bound num_tokens (every later step reads its bounds on the device).
-        max_cluster caps the CTAs of the plan kernels (0 = up to 8)."""
+        max_cluster caps the CTAs of the plan kernels (0 = up to 8).
+        With the device-side exchange nothing is read on the host either: the second value is the arena size, and
+        `payload` = (hidden_states, input_scales) lets the rows travel in the same launch as the expert ids
+        (`dispatch` is then a no-op)."""
         T = expert_indices.shape[0]
         ctx = self.context = self.get_context(T, num_global_tokens, num_stages, input_quanted)
         W, S, k = self.W, num_stages, self.top_k
@@ -137,6 +262,28 @@ class Scheduler:
             else:
                 ctx.n_recv = None
                 rows_bound = T
+        elif self.peer is not None:
+            pe = self.peer
+            if S > pe.S_max:
+                raise EpsError(f"Invalid num_stages: {S} for local_num_experts: {self.local_num_experts}")
+            pe.begin()
+            self._select_arenas()
+            pe.publish_plans(ctx.send_incl, ctx.coll_incl, S)
+            ctx.recv_incl = torch.empty((W * S,), dtype=torch.int32, device=self.device)
+            pe.recv_plans(S, ctx.recv_incl)
+            mask = PUT_META
+            ctx.eager = payload is not None
+            hidden = scales = None
+            if ctx.eager:
+                hidden, scales = payload
+                hidden = hidden.view(torch.uint8) if hidden.dtype == torch.float8_e4m3fn else hidden
+                if hidden.dtype != self.hidden_dtype:
+                    raise EpsError(f"hidden_states must have dtype {self.hidden_dtype}, got {hidden.dtype}")
+                mask |= PUT_HIDDEN | (PUT_SCALES if scales is not None else 0)
+            pe.put(FLAG_META, -1, mask, expert_indices, expert_scales, hidden, scales, ctx.send_map, ctx.send_incl, T, S)
+            pe.wait(FLAG_META)
+            ctx.n_recv = None
+            rows_bound = self.arena_rows
         else:
             # One all-gather carries both inclusive plans of every rank: what it sends (dispatch) and what it will
             # collect back (combine).  The rows this rank returns to peer p are the rows p collects from it, so the
@@ -155,11 +302,12 @@ class Scheduler:
                 raise EpsError("received rows exceed the arena")
         ctx.rows_bound = rows_bound
         # --- plan (reference scheduler.cu:286-353)
-        self._expand_for_comm(expert_indices, self.send_idx, ctx)
-        self._all2all(self.send_idx, self.recv_idx, ctx, -1, combine=False)
+        if self.peer is None:
+            self._expand_for_comm(expert_indices, self.send_idx, ctx)
+            self._all2all(self.send_idx, self.recv_idx, ctx, -1, combine=False)
         (ctx.excl, ctx.gemm_map, ctx.inv_gemm, ctx.scale_map, ctx.red_map, ctx.ret_incl) = ops.expert_plans(
             self.recv_idx, ctx.recv_incl, k, self.lo, self.hi, W, S, self.max_tok, max(rows_bound, 0),
-            max_cluster=max_cluster)
+            status=self.peer.status[2:] if self.peer is not None else None, max_cluster=max_cluster)
         return ctx.excl, (ctx.n_recv if ctx.n_recv is not None else rows_bound)
 
     # ------------------------------------------------------------------ data path
@@ -195,15 +343,32 @@ class Scheduler:
         host view of the plans; rows that stay on this rank are not counted.  A dispatched row is its FP8 (or bf16)
         hidden row + its scales + k expert ids + k gate weights; a returned row is bf16 hidden."""
         ctx = self.context
-        if self.W == 1 or ctx is None or ctx.host_dispatch is None:
+        if self.W == 1 or ctx is None:
             return 0, 0
-        sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, self.W, ctx.num_stages, stage)
+        if ctx.host_dispatch is None:
+            # device-side exchange: the plans never came to the host; read them now (synchronises: not for hot paths)
+            if self.peer is None:
+                return 0, 0
+            W, S = self.W, ctx.num_stages
+            if combine:
+                mine, theirs = ctx.ret_incl.cpu().numpy(), ctx.coll_incl.cpu().numpy()
+            else:
+                mine, theirs = ctx.send_incl.cpu().numpy(), ctx.recv_incl.cpu().numpy()
+            win = (_excl(mine.astype(np.int64)), mine.astype(np.int64), _excl(theirs.astype(np.int64)),
+                   theirs.astype(np.int64))
+            sl = stage_slices(win, W, S, stage)
+        else:
+            sl = stage_slices(ctx.host_combine if combine else ctx.host_dispatch, self.W, ctx.num_stages, stage)
+        return self._bytes_of(sl, combine)
+
+    def _bytes_of(self, sl, combine: bool):
         out_rows = sum(b - a for p, ((a, b), _) in enumerate(sl) if p != self.rank)
         in_rows = sum(d - c for p, (_, (c, d)) in enumerate(sl) if p != self.rank)
         if combine:
             row = self.hidden * 2
         else:
-            row = self.hidden * self.send_hidden.element_size() + self.scales_dim * 4 + self.top_k * 8
+            elem = torch.empty((), dtype=self.hidden_dtype).element_size()
+            row = self.hidden * elem + self.scales_dim * 4 + self.top_k * 8
         return out_rows * row, in_rows * row
 
     def prologue(self, expert_scales: torch.Tensor, hidden_states: torch.Tensor, input_scales=None,
@@ -214,6 +379,17 @@ class Scheduler:
         the same grouped exchange as the first `dispatch`; `finish_prologue()` must follow that dispatch."""
         ctx = self.context
         ctx.raw_input = raw_input if raw_input is not None else hidden_states
+        if self.peer is not None:
+            # device-side exchange: rows are read through the dispatch plan when they are sent; nothing to stage
+            h = hidden_states.view(torch.uint8) if hidden_states.dtype == torch.float8_e4m3fn else hidden_states
+            if h.dtype != self.hidden_dtype:
+                raise EpsError(f"hidden_states must have dtype {self.hidden_dtype}, got {h.dtype}")
+            if ctx.input_quanted and (input_scales is None or recv_input_scales is None or self.scales_dim == 0):
+                raise EpsError("input_quanted needs input_scales, recv_input_scales and input_scales_dim > 0")
+            ctx.src_hidden, ctx.src_scales = h, (input_scales if ctx.input_quanted else None)
+            ctx.src_idx_w = None
+            ctx.scales_out = recv_input_scales if ctx.input_quanted else None
+            return
         defer = defer_exchange and self.W > 1
         ctx.deferred = [] if defer else None
         self._expand_for_comm(expert_scales, self.send_w, ctx)
@@ -248,6 +424,15 @@ class Scheduler:
 
     def dispatch(self, stage_idx: int) -> None:
         ctx = self.context
+        if self.peer is not None:
+            if getattr(ctx, "eager", False):
+                return   # the rows travelled with the expert ids
+            pe = self.peer
+            mask = PUT_HIDDEN | (PUT_SCALES if ctx.src_scales is not None else 0)
+            pe.put(pe.flag_dispatch(stage_idx), stage_idx, mask, None, None, ctx.src_hidden, ctx.src_scales,
+                   ctx.send_map, ctx.send_incl, ctx.num_tokens, ctx.num_stages)
+            pe.wait(pe.flag_dispatch(stage_idx))
+            return
         items = [(self.send_hidden, self.recv_hidden, stage_idx)]
         if getattr(ctx, "deferred", None):
             items = ctx.deferred + items      # gate weights and input scales of ALL stages go with the first dispatch
@@ -261,12 +446,24 @@ class Scheduler:
         b0, b1 = (0, self.local_num_experts) if stage_idx < 0 else (eps_ * stage_idx, eps_ * (stage_idx + 1))
         g = gemm_input.view(torch.uint8) if gemm_input.dtype == torch.float8_e4m3fn else gemm_input
         ops.gather_rows(self.recv_hidden, g, ctx.gemm_map, self.top_k, ops.INT32_MAX, bounds=ctx.excl, b0=b0, b1=b1)
+        if self.peer is not None and getattr(ctx, "scales_out", None) is not None:
+            # the stage's input scales arrived with its rows: bring them to GEMM order too
+            ops.gather_rows(self.recv_scales, ctx.scales_out, ctx.gemm_map, self.top_k, ops.INT32_MAX,
+                            bounds=ctx.excl, b0=b0, b1=b1)
 
     def local_reduce(self, gemm_output: torch.Tensor, stage_idx: int, pre_weighted: bool = False) -> None:
         """Sums the rows of each received token over this rank's experts into the return buffer.
         pre_weighted=False: reference arithmetic (bf16(weight) * row, bf16 accumulate, local_reducer.cu:103-181).
         pre_weighted=True : rows already carry their gate weight (fused down-GEMM epilogue); fp32 accumulate."""
         ctx = self.context
+        if self.peer is not None:
+            if not pre_weighted:
+                raise EpsError("the device-side exchange returns pre-weighted rows (pre_weighted=True); the reference's "
+                               "bf16 arithmetic is available with transport 'nccl'")
+            pe = self.peer
+            pe.local_reduce_put(pe.flag_combine(stage_idx), gemm_output, ctx.red_map, ctx.ret_incl, ctx.num_stages,
+                                stage_idx, max(ctx.rows_bound, 0))
+            return
         if pre_weighted:
             ops.local_reduce(gemm_output, ctx.red_map, ctx.ret_incl, self.top_k, self.W, ctx.num_stages, stage_idx,
                              self.send_out, max_rows=max(ctx.rows_bound, 0))
@@ -275,6 +472,9 @@ class Scheduler:
                                  self.W, ctx.num_stages, stage_idx, self.send_out, max_rows=max(ctx.rows_bound, 0))
 
     def combine(self, stage_idx: int) -> None:
+        if self.peer is not None:
+            self.peer.wait(self.peer.flag_combine(stage_idx))   # the rows were stored by the peers' local_reduce
+            return
         self._all2all(self.send_out, self.recv_out, self.context, stage_idx, combine=True)
 
     def epilogue(self, output: torch.Tensor, shared: torch.Tensor | None = None, ref_arith: bool = True) -> None:

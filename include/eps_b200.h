@@ -338,6 +338,96 @@ int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const vo
 int epsb_gather_row_weights(const float* w_recv, const int32_t* gemm_map, const int32_t* excl, int num_experts,
                             int64_t max_rows, float* row_w, void* stream);
 
+/* ----------------------------------------------------------------------------
+ * Expert-parallel exchange over peer memory (one NVSwitch box, W <= 8 ranks).
+ * ref: CommBuffs arenas (src/communication/msccl_comm.cu:191-255), the plan
+ *      all-gather with flags and getRecvPlan (src/communication/alltoall_runner.cu:39-128),
+ *      the SM-copy all-to-all All2All<T> (alltoall_runner.cu:131-256, smChan_put in
+ *      src/communication/msccl_comm.cuh:166-183); fused with expandForComm
+ *      (src/scheduler/comm_expander.cu:118-215) on the way out and with localReduce
+ *      (src/scheduler/local_reducer.cu:103-211) on the way back.
+ *
+ * Every rank owns one symmetric REGION that all ranks of the box map (CUDA IPC):
+ * plan tables, flag words and the receive arenas.  After set-up nothing goes
+ * through the host: plans are stored into the peers' tables and announced with a
+ * flag, rows are stored by SM threads straight into the destination's arena at
+ * the offset the exchanged plans give, and each exchange ends with a flag at
+ * every peer.  Only peer STORES are used (no loads from peer memory, no TMA, no
+ * multicast).  Flags carry the call's epoch, which only grows; tables and
+ * dispatch arenas are double-buffered by epoch parity.
+ * Every spin is bounded: after timeout_ns (<= 0: EPSB_EXCHANGE_DEFAULT_TIMEOUT_NS)
+ * the kernel writes a code into status[0] (and the peer it waited for into
+ * status[1]) and returns; after a plan time-out the exchange of that call is
+ * empty (all counts 0), so the later kernels of the call are no-ops.
+ * -------------------------------------------------------------------------- */
+#define EPSB_MAX_PEERS 8
+#define EPSB_IPC_HANDLE_BYTES 64
+#define EPSB_EXCHANGE_DEFAULT_TIMEOUT_NS 2000000000ll
+#define EPSB_EXCHANGE_TIMEOUT_PLANS 61  /* status code: a peer's plans did not arrive */
+#define EPSB_EXCHANGE_ROWS_EXCEEDED 62  /* status code: the peers announce more rows than the arena holds */
+#define EPSB_EXCHANGE_TIMEOUT_DATA 70   /* status code base: + flag slot of the exchange that did not complete */
+
+/* Symmetric memory.  epsb_symm_alloc: cudaMalloc + zero fill + IPC handle (64 bytes, to be sent to the peers by
+ * whatever channel the host has); epsb_symm_open maps a peer's handle into this process.  These four functions
+ * allocate / free device memory and synchronise; they belong to set-up and tear-down. */
+int epsb_symm_alloc(int64_t bytes, void** ptr, uint8_t* handle64);
+int epsb_symm_open(const uint8_t* handle64, void** ptr);
+int epsb_symm_close(void* ptr);
+int epsb_symm_free(void* ptr);
+
+typedef struct epsb_exchange epsb_exchange_t;
+
+/* Size of one rank's region for (W ranks, max_tok tokens per rank, up to S_max stages, top-k, hidden size H with
+ * elements of hidden_elem_bytes (1 = e4m3 codes, 2 = bf16), scales_dim fp32 scales per row (0 = none)): arenas of
+ * max_tok * W rows each, as the reference sizes them (msccl_comm.cu:191-199). */
+int epsb_exchange_region_bytes(int W, int max_tok, int S_max, int k, int64_t H, int hidden_elem_bytes, int scales_dim,
+                               int64_t* bytes);
+/* peer_regions: host array of W device pointers, entry r = rank r's region as mapped into this process (entry
+ * `rank` = this rank's own allocation).  Allocates a few hundred bytes of device scratch (set-up). */
+int epsb_exchange_create(int rank, int W, int max_tok, int S_max, int k, int64_t H, int hidden_elem_bytes,
+                         int scales_dim, void* const* peer_regions, epsb_exchange_t** out);
+int epsb_exchange_destroy(epsb_exchange_t* x);
+/* Starts the next call: advances the epoch (host side, no launch).  Every rank must go through the same sequence
+ * of begin / publish / recv_plans / put / wait / local_reduce_put calls. */
+int epsb_exchange_begin(epsb_exchange_t* x, int* epoch);
+
+#define EPSB_ARENA_IDX 0       /* int32 [rows, k]   received expert ids */
+#define EPSB_ARENA_WEIGHTS 1   /* fp32  [rows, k]   received gate weights */
+#define EPSB_ARENA_HIDDEN 2    /* [rows, H]         received hidden rows */
+#define EPSB_ARENA_SCALES 3    /* fp32  [rows, scales_dim] */
+#define EPSB_ARENA_OUT 4       /* bf16  [rows, H]   returned partial rows (collect arena) */
+#define EPSB_ARENA_RECV_PLAN 5 /* int32 [W * S_max] the receive plan epsb_exchange_recv_plans derived */
+/* Device address of one of this rank's arenas; parity = epoch & 1 for the double-buffered ones. */
+int epsb_exchange_arena(epsb_exchange_t* x, int which, int parity, void** ptr);
+
+/* send_incl / coll_incl [W*S]: the plans epsb_source_plans wrote.  One CTA; stores + one flag per peer. */
+int epsb_exchange_publish_plans(epsb_exchange_t* x, const int32_t* send_incl, const int32_t* coll_incl, int S,
+                                void* stream);
+/* Waits for every peer's plans, then derives the receive plan (also copied to recv_incl [W*S] if not NULL;
+ * ref getRecvPlan, alltoall_runner.cu:60-101) and this rank's landing offsets at every peer for both directions. */
+int epsb_exchange_recv_plans(epsb_exchange_t* x, int S, int32_t* recv_incl, int32_t* status, int64_t timeout_ns,
+                             void* stream);
+
+/* Flag slots of the data exchanges (slot 0 is the plans'). */
+#define EPSB_FLAG_META 1
+#define EPSB_FLAG_DISPATCH(stage) (2 + (stage))
+#define EPSB_FLAG_COMBINE(S_max, stage) (2 + (S_max) + (stage))
+#define EPSB_PUT_META 1    /* expert ids + gate weights */
+#define EPSB_PUT_SCALES 2
+#define EPSB_PUT_HIDDEN 4
+/* Permute-on-send: rows of the send order whose stage is `stage` (all stages if < 0) are read through send_map
+ * (row i is token send_map[i] % T) and stored into their destination's arenas; `mask` selects the arrays.  The
+ * last CTA releases flag `flag_slot` at every peer.  idx [T,k], weights [T,k], hidden [T,H], scales [T,scales_dim]. */
+int epsb_exchange_put(epsb_exchange_t* x, int flag_slot, int stage, int mask, const int32_t* idx, const float* weights,
+                      const void* hidden, const float* scales, const int32_t* send_map, const int32_t* send_incl, int T,
+                      int S, void* stream);
+/* Consumer side of an exchange: bounded wait for flag `flag_slot` of every peer (one warp). */
+int epsb_exchange_wait(epsb_exchange_t* x, int flag_slot, int32_t* status, int64_t timeout_ns, void* stream);
+/* Return trip: epsb_local_reduce (pre-weighted rows, fp32 accumulation) whose output row lands directly in the
+ * source rank's collect arena; then flag `flag_slot` at every peer. */
+int epsb_exchange_local_reduce_put(epsb_exchange_t* x, int flag_slot, const void* y, const int32_t* red_map,
+                                   const int32_t* ret_incl, int S, int stage, int64_t max_rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

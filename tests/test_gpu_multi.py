@@ -1,4 +1,5 @@
-"""Expert parallelism over 2 GPUs (NCCL): every rank's layer output against the fp32 oracle of the global layer.
+"""Expert parallelism over 2 GPUs, both transports (this library's peer-store kernels over CUDA IPC, and grouped NCCL
+send/recv): every rank's layer output against the fp32 oracle of the global layer.
 Skipped on machines with fewer than two GPUs."""
 import os
 import sys
@@ -13,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, case, q):
+def _worker(rank, world, port, case, transport, q):
     try:
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -45,17 +46,19 @@ def _worker(rank, world, port, case, q):
             a, b = workloads.make_expert_weights(cfg, -1, inter=sh)
             shared = (*ops.quant_block128(a.unsqueeze(0).to(dev)), *ops.quant_block128(b.unsqueeze(0).to(dev)))
             ref_shared = (*orc.quant_block128(a.unsqueeze(0).float().numpy()), *orc.quant_block128(b.unsqueeze(0).float().numpy()))
-        comm = Communicator(None, CommunicatorParams(rank, world, world))
+        comm = Communicator(None, CommunicatorParams(rank, world, world), transport=transport)
+        assert comm.transport == transport
         Tr = T + 5 * rank   # ragged token counts per rank
         layer = MoELayerFP8(H, I, E, k, T + 5 * world, gq, gs, dq, ds, comm=comm, shared=shared, num_stages=S)
         x = workloads.make_tokens(cfg, rank, Tr)
         idx, w = workloads.make_routing(cfg, rank, Tr)
-        for _ in range(2):  # second call reuses arenas and plans buffers
+        for _ in range(3):  # later calls reuse the arenas (both parities of the device-side exchange) and plan buffers
             out = layer.forward(x.to(dev), idx.to(dev), w.to(dev))
             ctx = layer.sched.context
-            # the combine windows the host derived from the all-gathered plans == the device's return plan
-            assert np.array_equal(ctx.ret_incl.cpu().numpy(), ctx.host_combine[1]), "return plan mismatch"
-            assert np.array_equal(ctx.coll_incl.cpu().numpy(), ctx.host_combine[3]), "collect plan mismatch"
+            if transport == "nccl":
+                # the combine windows the host derived from the all-gathered plans == the device's return plan
+                assert np.array_equal(ctx.ret_incl.cpu().numpy(), ctx.host_combine[1]), "return plan mismatch"
+                assert np.array_equal(ctx.coll_incl.cpu().numpy(), ctx.host_combine[3]), "collect plan mismatch"
         torch.cuda.synchronize()
         layer.check_status()
         rq, rs = orc.quant_block128(gu.float().numpy())
@@ -65,6 +68,7 @@ def _worker(rank, world, port, case, q):
         got = out.float().cpu().numpy()
         rms = float(np.sqrt(np.mean(want ** 2)))
         worst = float(np.max(np.abs(got - want) / (2e-2 * rms + 2.0 ** -8 * np.abs(want))))
+        layer.sched.destroy()
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok" if worst <= 1.0 else f"worst err/bound {worst:.3f}"))
@@ -74,8 +78,9 @@ def _worker(rank, world, port, case, q):
         q.put((rank, traceback.format_exc()))
 
 
+@pytest.mark.parametrize("transport", ["ipc", "nccl"])
 @pytest.mark.parametrize("case", [(64, 512, 256, 8, 2, 0, 0, 1), (100, 1024, 512, 8, 4, 4, 256, 2), (200, 2048, 1408, 16, 4, 0, 0, 4)])
-def test_layer_ep2_vs_oracle(case):
+def test_layer_ep2_vs_oracle(case, transport):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from eps_b200 import build
@@ -86,8 +91,8 @@ def test_layer_ep2_vs_oracle(case):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + (os.getpid() + case[0]) % 1500
-    procs = [ctx.Process(target=_worker, args=(r, world, port, case, q)) for r in range(world)]
+    port = 29700 + (os.getpid() + case[0] + (700 if transport == "ipc" else 0)) % 1500
+    procs = [ctx.Process(target=_worker, args=(r, world, port, case, transport, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
@@ -120,7 +125,7 @@ def _fastep_worker(rank, world, port, q):
         rng = np.random.default_rng(50 + rank)
         idx, w = random_routing(rng, T, k, E, 3)
         x = torch.randn((T, H), generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16)
-        comm = Communicator(None, CommunicatorParams(rank, world, world))
+        comm = Communicator(None, CommunicatorParams(rank, world, world), transport="nccl")
         a2a = AllToAll(k, E, H, 256, comm)
         excl = torch.empty((EL + 1,), dtype=torch.int32, device=dev)
         expert_x = torch.zeros((256 * k, H), dtype=torch.bfloat16, device=dev)
