@@ -10,8 +10,8 @@
 //     ragged tile list built on the device from the expert prefix sum;
 //   * tile = 128 rows (tokens) x 256 weight rows, K step 128 (= one 128-byte
 //     swizzle atom of e4m3, four tcgen05.mma of K=32);
-//   * warp 0 issues TMA loads into a 3-stage shared-memory ring, warp 1 issues
-//     the MMAs into one of two 256-column TMEM buffers, warps 4..11 (two
+//   * warp 0 issues TMA loads into a 3-stage shared-memory ring, warps 1 and 2 issue
+//     the MMAs of the even / odd K steps into one of two 256-column TMEM buffers, warps 4..11 (two
 //     warpgroups) drain a TMEM buffer per K step with tcgen05.ld and fold it
 //     into fp32 register accumulators multiplied by a_scale[row,kb]*b_scale[nb,kb]
 //     (the scales are plain fp32, so the hardware's power-of-two block scaling
@@ -325,14 +325,21 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
         const uint64_t t0 = global_ns();
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
       }
-    } else if (warp == 1 && lane == 0) {
-      // ------------------------------------------------ MMA issuer
+    } else if ((warp == 1 || warp == 2) && lane == 0) {
+      // ------------------------------------------------ MMA issuers: warp 1 takes the even K steps (accumulator
+      // buffer 0), warp 2 the odd ones (buffer 1).  A K step's MMAs accumulate from scratch into their own buffer, so
+      // the two threads need no order between them.  One thread alone cannot keep the tensor pipe fed: its chain per
+      // K step (wait for the buffer, wait for the stage, four MMAs whose issue is paced by the pipe, two commits) has
+      // ~500 cycles of barrier latency in it during which nothing is queued behind the MMAs in flight; with two
+      // threads the waits of step it+1 run while the MMAs of step it execute.
+      const uint32_t me = (uint32_t)(warp - 1);
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int tail = locate_tile(t, p, sm).tail;
         const uint32_t idesc_tail = f8_idesc(128, tail);
         for (int kb = 0; kb < KB; kb++, it++) {
+          if ((it & 1u) != me) continue;
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           const int buf = it & 1;
