@@ -24,6 +24,7 @@ SIGNATURES = {
     "epsb_dequant_1x128": [_P, _P, _L, _L, _P, _P],
     "epsb_quant_block128": [_P, _L, _L, _L, _P, _P, _P],
     "epsb_source_plans": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
+    "epsb_zero_plan": [_P, _P, _I, _I, _P, _P],
     "epsb_recv_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
     "epsb_expert_plans": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "epsb_expert_plans_noalloc": [_P, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -44,7 +45,17 @@ SIGNATURES = {
     "epsb_rms_norm": [_P, _P, _P, c_float, _L, _L, _P],
     "epsb_router_topk_sigmoid": [_P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
+    "epsb_grouped_gemm_bf16": [_P, _P, _P, _I, _L, _L, _L, _P, _P, _I, _P],
     "epsb_gather_row_weights": [_P, _P, _P, _I, _L, _P, _P],
+    "epsb_oep_arrange_plan": [_P, _L, _L, _I, _P, _P, _P, _P],
+    "epsb_exchange_put_ids": [_P, _I, _P, _P, _P, _L, _P],
+    "epsb_exchange_lookup_put": [_P, _I, _P, _L, _L, _P],
+    "epsb_oep_scatter": [_P, _P, _L, _L, _L, _I, _P, _P],
+    "epsb_tpdp_region_bytes": [_L, _L, _P],
+    "epsb_tpdp_signal": [_P, _I, _I, _L, _L, _I, _I, _P],
+    "epsb_tpdp_wait": [_P, _I, _L, _L, _I, _I, _P, _L, _P],
+    "epsb_tpdp_all_gather_put": [_P, _I, _I, _L, _L, _L, _L, _I, _I, _P],
+    "epsb_tpdp_reduce_scatter_sum": [_P, _I, _I, _L, _L, _L, _L, _I, _I, _P],
     "epsb_symm_alloc": [_L, _P, _P],
     "epsb_symm_open": [_P, _P],
     "epsb_symm_close": [_P],

@@ -60,7 +60,7 @@ Layout make_layout(int max_tok, int W, int S, int k, int64_t H, int hidden_elem,
   off = align256(off + (int64_t)(2 + 2 * S) * W * 4);
   l.idx_bytes = align256(rows * k * 4);
   l.wts_bytes = align256(rows * k * 4);
-  l.hidden_bytes = align256(rows * H * hidden_elem);
+  l.hidden_bytes = hidden_elem > 0 ? align256(rows * H * hidden_elem) : 0;   // 0: an exchange of ids and return rows only
   l.scales_bytes = align256(rows * (scales_dim > 0 ? scales_dim : 1) * 4);
   l.idx = off;
   off += 2 * l.idx_bytes;
@@ -404,6 +404,47 @@ local_reduce_put_kernel(Peers peers, const uint8_t* __restrict__ y, const int32_
   signal_when_grid_done(peers, off_flags, flag_slot, W, rank, epoch, cta_counter);
 }
 
+// ---------------------------------------------------------------- fast_oep: ids out, table rows back
+
+// Position pos of the arranged order (ids grouped by owner rank) goes to owner p's id arena.
+__global__ void __launch_bounds__(kXThreads)
+put_ids_kernel(Peers peers, const int32_t* __restrict__ ids, const int32_t* __restrict__ send_map,
+               const int32_t* __restrict__ send_incl, const int32_t* __restrict__ disp_off, int64_t off_idx,
+               int64_t off_flags, int flag_slot, int W, int rank, uint32_t epoch, int32_t* cta_counter) {
+  const int n_sent = send_incl[W - 1];
+  for (int pos = blockIdx.x * kXThreads + threadIdx.x; pos < n_sent; pos += gridDim.x * kXThreads) {
+    int p = 0;
+    while (p < W - 1 && pos >= send_incl[p]) p++;
+    const int begin = p == 0 ? 0 : send_incl[p - 1];
+    reinterpret_cast<int32_t*>(peers.base[p] + off_idx)[disp_off[p] + (pos - begin)] = ids[send_map[pos]];
+  }
+  signal_when_grid_done(peers, off_flags, flag_slot, W, rank, epoch, cta_counter);
+}
+
+// The owner side: received id q (from source r) selects a row of this rank's table shard; the row is stored at
+// position comb_off[r] + (q - block begin) of r's row arena, i.e. at the id's position in r's arranged order
+// (reference lookupKernel + the combine All2All, fast_oep_kernels.cu:186-216, fast_oep.cu:105-133).
+__global__ void __launch_bounds__(kXThreads)
+lookup_put_kernel(Peers peers, const int32_t* __restrict__ recv_ids, const int32_t* __restrict__ recv_incl,
+                  const int32_t* __restrict__ comb_off, const uint8_t* __restrict__ table, int64_t size_per_rank,
+                  int64_t row_bytes, int64_t off_out, int64_t off_flags, int flag_slot, int W, int rank, uint32_t epoch,
+                  int32_t* cta_counter) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kXWarps + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * kXWarps;
+  const int vecs = (int)(row_bytes >> 4);
+  const int R = recv_incl[W - 1];
+  for (int64_t q = warp; q < R; q += n_warps) {
+    int r = 0;
+    while (r < W - 1 && q >= recv_incl[r]) r++;
+    const int64_t begin = r == 0 ? 0 : recv_incl[r - 1];
+    const int64_t local = (int64_t)recv_ids[q] % size_per_rank;
+    copy_row16(table + local * row_bytes, peers.base[r] + off_out + ((int64_t)comb_off[r] + (q - begin)) * row_bytes,
+               vecs, lane);
+  }
+  signal_when_grid_done(peers, off_flags, flag_slot, W, rank, epoch, cta_counter);
+}
+
 Peers peers_of(const epsb_exchange* x) {
   Peers p;
   for (int i = 0; i < kMaxPeers; i++) p.base[i] = x->peer[i < x->W ? i : 0];
@@ -477,7 +518,7 @@ static int check_shape(int W, int max_tok, int S, int k, int64_t H, int hidden_e
   EPSB_REQUIRE(max_tok >= 0 && S >= 1 && k >= 1 && k <= 32, EPSB_ERR_INVALID, "bad sizes max_tok=%d S=%d k=%d", max_tok,
                S, k);
   EPSB_REQUIRE((int64_t)W * S <= 1024, EPSB_ERR_INVALID, "ep_world_size * num_stages is too big.");
-  EPSB_REQUIRE(H > 0 && H % 8 == 0 && (hidden_elem == 1 || hidden_elem == 2) && (H * hidden_elem) % 16 == 0,
+  EPSB_REQUIRE(H > 0 && H % 8 == 0 && hidden_elem >= 0 && hidden_elem <= 2 && (H * hidden_elem) % 16 == 0,
                EPSB_ERR_INVALID, "hidden size %lld x %d bytes is not a multiple of 16 bytes", (long long)H, hidden_elem);
   EPSB_REQUIRE(scales_dim >= 0, EPSB_ERR_INVALID, "scales_dim %d is negative", scales_dim);
   return EPSB_OK;
@@ -587,6 +628,8 @@ extern "C" int epsb_exchange_put(epsb_exchange_t* x, int flag_slot, int stage, i
                "EPSB_PUT_META needs idx and weights");
   EPSB_REQUIRE(!(mask & EPSB_PUT_HIDDEN) || T == 0 || (hidden != nullptr && ((uintptr_t)hidden & 15) == 0),
                EPSB_ERR_INVALID, "EPSB_PUT_HIDDEN needs a 16-byte aligned hidden buffer");
+  EPSB_REQUIRE(!(mask & EPSB_PUT_HIDDEN) || x->hidden_elem > 0, EPSB_ERR_INVALID,
+               "this exchange was created without hidden arenas");
   EPSB_REQUIRE(!(mask & EPSB_PUT_SCALES) || T == 0 || x->scales_dim == 0 || scales != nullptr, EPSB_ERR_INVALID,
                "EPSB_PUT_SCALES needs scales");
   const int par = x->epoch & 1;
@@ -643,4 +686,38 @@ extern "C" int epsb_exchange_local_reduce_put(epsb_exchange_t* x, int flag_slot,
                                                             x->k, x->W, S, stage, x->H, x->rank, (uint32_t)x->epoch,
                                                             x->dev + 1);
   return check_launch("exchange_local_reduce_put");
+}
+
+// ---------------------------------------------------------------- fast_oep entry points
+
+extern "C" int epsb_exchange_put_ids(epsb_exchange_t* x, int flag_slot, const int32_t* ids, const int32_t* send_map,
+                                     const int32_t* send_incl, int64_t n, void* stream) {
+  EPSB_REQUIRE(x != nullptr && x->epoch > 0, EPSB_ERR_INVALID, "call epsb_exchange_begin first");
+  EPSB_REQUIRE(flag_slot >= 1 && flag_slot < 2 + 2 * x->S, EPSB_ERR_INVALID, "bad flag slot %d", flag_slot);
+  EPSB_REQUIRE(x->k == 1, EPSB_ERR_INVALID, "an id exchange needs an exchange created with k = 1");
+  EPSB_REQUIRE(n >= 0 && n <= (int64_t)(x->max_tok > 0 ? x->max_tok : 1) * x->W, EPSB_ERR_INVALID,
+               "%lld ids exceed the arena", (long long)n);
+  const int par = x->epoch & 1;
+  int64_t blocks = (n + kXThreads - 1) / kXThreads;
+  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+  if (blocks < 1) blocks = 1;
+  put_ids_kernel<<<(int)blocks, kXThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      peers_of(x), ids, send_map, send_incl, x->dev + kDevWords, x->lay.idx + par * x->lay.idx_bytes, x->lay.flags,
+      flag_slot, x->W, x->rank, (uint32_t)x->epoch, x->dev + 0);
+  return check_launch("exchange_put_ids");
+}
+
+extern "C" int epsb_exchange_lookup_put(epsb_exchange_t* x, int flag_slot, const void* table, int64_t size_per_rank,
+                                        int64_t max_rows, void* stream) {
+  EPSB_REQUIRE(x != nullptr && x->epoch > 0, EPSB_ERR_INVALID, "call epsb_exchange_begin first");
+  EPSB_REQUIRE(flag_slot >= 1 && flag_slot < 2 + 2 * x->S, EPSB_ERR_INVALID, "bad flag slot %d", flag_slot);
+  EPSB_REQUIRE(x->k == 1 && size_per_rank > 0 && table != nullptr && ((uintptr_t)table & 15) == 0, EPSB_ERR_INVALID,
+               "bad table / size_per_rank");
+  const int par = x->epoch & 1;
+  const int64_t n = (int64_t)x->W * x->S;
+  const int32_t* recv_ids = reinterpret_cast<const int32_t*>(x->peer[x->rank] + x->lay.idx + par * x->lay.idx_bytes);
+  lookup_put_kernel<<<grid_for_rows(max_rows > 0 ? max_rows : 1), kXThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      peers_of(x), recv_ids, x->dev + kDevWords + 2 * n, x->dev + kDevWords + n, static_cast<const uint8_t*>(table),
+      size_per_rank, x->H * 2, x->lay.out, x->lay.flags, flag_slot, x->W, x->rank, (uint32_t)x->epoch, x->dev + 1);
+  return check_launch("exchange_lookup_put");
 }

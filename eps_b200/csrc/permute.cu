@@ -113,6 +113,25 @@ gather_row_weights_kernel(const float* __restrict__ w_recv, const int32_t* __res
     row_w[d] = w_recv[gemm_map[d]];
 }
 
+// out[dst(i), :] = rows[mapping[i], :] for mapping[i] >= 0; dst(i) = i, or with do_permute the n-gram-major position
+// i / n_grams + (i % n_grams) * (n / n_grams) (reference scatterKernel, fast_oep_kernels.cu:218-245).
+__global__ void __launch_bounds__(kMoveThreads)
+oep_scatter_kernel(const uint8_t* __restrict__ rows, const int32_t* __restrict__ mapping, int64_t n, int64_t row_bytes,
+                   int64_t n_grams, int do_permute, uint8_t* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kMoveWarps + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * kMoveWarps;
+  const int vecs = (int)(row_bytes >> 4);
+  const int64_t batch = n / n_grams;
+  for (int64_t i = warp; i < n; i += n_warps) {
+    const int32_t m = __ldg(mapping + i);
+    if (m < 0) continue;
+    const int64_t d = do_permute ? i / n_grams + (i % n_grams) * batch : i;
+    copy_row(reinterpret_cast<const uint4*>(rows + (int64_t)m * row_bytes), reinterpret_cast<uint4*>(out + d * row_bytes),
+             vecs, lane);
+  }
+}
+
 int move_grid(int64_t rows) {
   int64_t want = (rows + kMoveWarps - 1) / kMoveWarps;
   const int64_t cap = (int64_t)sm_count() * 8;
@@ -168,6 +187,18 @@ extern "C" int epsb_scatter_rows(const void* src, void* dst, const int32_t* map,
   scatter_rows_kernel<<<move_grid(n), kMoveThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)src, (uint8_t*)dst, map, div, n, row_bytes);
   return check_launch("scatter_rows");
+}
+
+extern "C" int epsb_oep_scatter(const void* rows, const int32_t* mapping, int64_t n, int64_t row_bytes, int64_t n_grams,
+                                int do_permute, void* out, void* stream) {
+  int rc = check_rows(rows, out, row_bytes);
+  if (rc) return rc;
+  EPSB_REQUIRE(n_grams > 0 && (!do_permute || n % n_grams == 0), EPSB_ERR_INVALID,
+               "n_grams %lld does not divide %lld ids", (long long)n_grams, (long long)n);
+  if (n <= 0) return EPSB_OK;
+  oep_scatter_kernel<<<move_grid(n), kMoveThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint8_t*)rows, mapping, n, row_bytes, n_grams, do_permute, (uint8_t*)out);
+  return check_launch("oep_scatter");
 }
 
 extern "C" int epsb_arrange_rows(const void* src, void* dst, const int32_t* src_off, const int32_t* rows,

@@ -320,6 +320,18 @@ source_plans_kernel(const int32_t* __restrict__ idx, const float* __restrict__ w
   write_stage_sums(s, W, EL, S, coll_incl);
 }
 
+// ------------------------------------------------------------------ S6 alone (callers that plan the sends first)
+
+__global__ void zero_plan_kernel(const int32_t* __restrict__ idx, const float* __restrict__ weights, int T, int k,
+                                 float* __restrict__ zero_scale) {
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) {
+    float z = 0.0f;
+    for (int j = 0; j < k; j++)
+      if (idx[(size_t)t * k + j] < 0) z += weights[(size_t)t * k + j];
+    zero_scale[t] = z;
+  }
+}
+
 // ------------------------------------------------------------------ S2 receive plan
 
 __global__ void __launch_bounds__(kPlanThreads, 1)
@@ -511,6 +523,39 @@ fastep_plan_kernel(const int32_t* __restrict__ ag, int my_rank, int W, int E, in
   }
 }
 
+// ------------------------------------------------------------------ fast_oep: ids grouped by owner rank
+
+struct OepArrangeProblem {
+  const int32_t* ids;
+  int32_t* mapping;
+  int32_t* send_map;
+  int32_t size_per_rank;
+  int W;
+  __device__ int slots() const { return 1; }
+  __device__ int key(int i, int) const {
+    const int id = ids[i];
+    if (id < 0) return -1;
+    const int r = id / size_per_rank;
+    return r < W ? r : -1;
+  }
+  __device__ void emit(int i, int, int out) const {
+    mapping[i] = out;
+    send_map[out] = i;
+  }
+  __device__ void skip(int i, int) const { mapping[i] = -1; }
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+oep_arrange_plan_kernel(const int32_t* __restrict__ ids, int n, int32_t size_per_rank, int W, int32_t* send_incl,
+                        int32_t* mapping, int32_t* send_map) {
+  extern __shared__ int32_t plan_smem[];
+  SortScratch s = carve(plan_smem, W);
+  OepArrangeProblem op{ids, mapping, send_map, size_per_rank, W};
+  stable_bucket_sort(op, n, W, s);
+  if (!cluster_leader()) return;
+  for (int r = threadIdx.x; r < W; r += kPlanThreads) send_incl[r] = s.base[r] + s.total[r];
+}
+
 // ---------------------------------------------------------------- scratch that nobody has to allocate
 
 // Backing store of epsb_expert_plans_noalloc: the inverse GEMM map (one int32 per received (row, slot)).
@@ -600,6 +645,15 @@ extern "C" int epsb_source_plans(const int32_t* idx, const float* weights, int T
                         send_incl, glob_map, coll_incl, zero_scale, cache ? (int)per_cta : 0);
 }
 
+extern "C" int epsb_zero_plan(const int32_t* idx, const float* weights, int T, int k, float* zero_scale, void* stream) {
+  EPSB_REQUIRE(T >= 0 && k > 0, EPSB_ERR_INVALID, "bad sizes T=%d k=%d", T, k);
+  if (T == 0) return EPSB_OK;
+  int blocks = (T + 255) / 256;
+  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+  zero_plan_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(idx, weights, T, k, zero_scale);
+  return check_launch("zero_plan");
+}
+
 extern "C" int epsb_recv_plan(const int32_t* gathered, int my_rank, int W, int S, int32_t* recv_incl,
                               int32_t* remote_offset, int32_t* total_rows, void* stream) {
   EPSB_REQUIRE(W > 0 && S > 0 && my_rank >= 0 && my_rank < W, EPSB_ERR_INVALID, "bad rank/world %d/%d", my_rank, W);
@@ -663,6 +717,23 @@ extern "C" int epsb_fastep_expand_plan(const int32_t* idx, int T, int k, int E, 
   if (rc) return rc;
   return launch_cluster(fastep_expand_plan_kernel, cluster_size_for((int64_t)T * k), smem,
                         static_cast<cudaStream_t>(stream), "fastep_expand_plan", idx, T, k, E, excl, mapping);
+}
+
+extern "C" int epsb_oep_arrange_plan(const int32_t* ids, int64_t n, int64_t size_per_rank, int W, int32_t* send_incl,
+                                     int32_t* mapping, int32_t* send_map, void* stream) {
+  EPSB_REQUIRE(n >= 0 && n < (1ll << 31) && size_per_rank > 0 && size_per_rank < (1ll << 31) && W > 0 &&
+                   W <= kMaxBuckets,
+               EPSB_ERR_INVALID, "bad sizes n=%lld size_per_rank=%lld W=%d", (long long)n, (long long)size_per_rank, W);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    cudaMemsetAsync(send_incl, 0, sizeof(int32_t) * W, st);
+    return check_launch("oep_arrange_plan(n=0)");
+  }
+  const size_t smem = sort_smem_bytes(W);
+  int rc = set_smem((const void*)oep_arrange_plan_kernel, smem);
+  if (rc) return rc;
+  return launch_cluster(oep_arrange_plan_kernel, cluster_size_for(n), smem, st, "oep_arrange_plan", ids, (int)n,
+                        (int32_t)size_per_rank, W, send_incl, mapping, send_map);
 }
 
 extern "C" int epsb_fastep_plan(const int32_t* all_gathered, int my_rank, int W, int E, int32_t* remote_recv_plan,

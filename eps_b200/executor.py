@@ -1,8 +1,8 @@
 """Executors: the host-side mirror of python/eps/executor (AokGroupedGemm, silu).
 
 The reference's `AokGroupedGemm.run(A, B, B_scale, exclusive_sum, num_tokens_hint)` asserts `B_scale is None`
-(bf16 x bf16 on sm_90a).  Here `B_scale` selects the FP8 block-scaled tcgen05 GEMM (A as e4m3 codes + `A_scale`);
-the bf16 path of the reference is not part of this build and raises.
+(bf16 x bf16 on sm_90a).  Here `B_scale is None` runs the bf16 tcgen05 grouped GEMM, and a `B_scale` selects the FP8
+block-scaled one (A as e4m3 codes + `A_scale`).
 """
 from __future__ import annotations
 
@@ -25,14 +25,16 @@ class AokGroupedGemm:
 
     def run(self, A: torch.Tensor, B: torch.Tensor, B_scale: torch.Tensor, exclusive_sum: torch.Tensor,
             num_tokens_hint: int, A_scale: torch.Tensor | None = None) -> torch.Tensor:
-        """C[rows of expert e] = A[rows] @ B[e]^T with 1x128 / 128x128 scales -> bf16 [max_num_tokens, N]."""
-        if B_scale is None or A_scale is None:
-            raise EpsError("this build provides the FP8 block-scaled grouped GEMM: pass e4m3 A/B with A_scale and "
-                           "B_scale (the reference's bf16 x bf16 sm_90a GEMM is not included)")
+        """C[rows of expert e] = A[rows] @ B[e]^T -> bf16 [max_num_tokens, N]; bf16 operands when B_scale is None,
+        e4m3 codes with 1x128 / 128x128 scales otherwise."""
         if B.shape[0] != self.num_local_experts:
             raise EpsError(f"B holds {B.shape[0]} experts, executor was created for {self.num_local_experts}")
         if self.status is None or self.status.device != A.device:
             self.status = torch.zeros(4, dtype=torch.int32, device=A.device)
+        if B_scale is None:
+            return ops.grouped_gemm_bf16(A, B, exclusive_sum, status=self.status)
+        if A_scale is None:
+            raise EpsError("the FP8 grouped GEMM needs A_scale next to B_scale")
         return ops.grouped_gemm_fp8(ops.GEMM_PLAIN, A, A_scale, B, B_scale, exclusive_sum, status=self.status)
 
     def run_gate_up_swiglu(self, A, A_scale, B, B_scale, exclusive_sum):

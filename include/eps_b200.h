@@ -132,6 +132,11 @@ int epsb_source_plans(const int32_t* idx, const float* weights, int T, int k, in
                       int32_t* send_incl, int32_t* glob_map, int32_t* coll_incl, float* zero_scale, int max_cluster,
                       void* stream);
 
+/* The zero-expert plan alone, for callers that learn the gate weights after the sends were planned (the reference
+ * computes it in Scheduler::plan, after rendezvous): zero_scale[t] = sum of weights[t,j] over slots with idx[t,j] < 0,
+ * in slot order.  ref: zeroReducePlanKernel (src/scheduler/zero_reducer.cu:11-32). */
+int epsb_zero_plan(const int32_t* idx, const float* weights, int T, int k, float* zero_scale, void* stream);
+
 /* Receive plan from the all-gathered send plans.
  * ref: AlltoallRunner::plan -> getRecvPlan<512>
  *      (src/communication/alltoall_runner.cuh:79-103, alltoall_runner.cu:60-101).
@@ -333,6 +338,16 @@ int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const vo
                              const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
                              const float* row_w, int32_t* status, int tile_tokens, int sm_count, void* stream);
 
+/* bf16 x bf16 -> bf16 grouped GEMM (tcgen05 kind::f16, accumulators resident in TMEM over the whole K extent):
+ * for local expert e, C[m,:] = A[m,:] * B[e]^T over rows [excl[e], excl[e+1]), fp32 accumulation, one rounding.
+ * ref: AokGroupedGemm::run (src/executor/aok_grouped_gemm.cu:22-37), the op executor.aok_run
+ *      (src/executor/bindings/aok_grouped_gemm_ops.cu:39-84), SM90_GROUPED_GEMM::Launch
+ *      (src/gemm/aok_grouped_gemm/src/operations/hopper_grouped_gemm_kernel.h:322-400; alpha 1, beta 0).
+ * A [max_rows, K] bf16 row-major, B [EL, N, K] bf16 (K contiguous), C [max_rows, N] bf16.  K % 64 == 0, N % 128 == 0.
+ * excl, status, sm_count as in epsb_grouped_gemm_fp8.  No workspace (aok_get_workspace_size is 0). */
+int epsb_grouped_gemm_bf16(const void* A, const void* B, const int32_t* excl, int num_experts, int64_t max_rows,
+                           int64_t N, int64_t K, void* C, int32_t* status, int sm_count, void* stream);
+
 /* Gathers the per-GEMM-row gate weight: row_w[d] = w_recv[gemm_map[d]] for
  * d < excl[EL] (w_recv is [R,k] flat, gemm_map holds row*k+slot). */
 int epsb_gather_row_weights(const float* w_recv, const int32_t* gemm_map, const int32_t* excl, int num_experts,
@@ -427,6 +442,70 @@ int epsb_exchange_wait(epsb_exchange_t* x, int flag_slot, int32_t* status, int64
  * source rank's collect arena; then flag `flag_slot` at every peer. */
 int epsb_exchange_local_reduce_put(epsb_exchange_t* x, int flag_slot, const void* y, const int32_t* red_map,
                                    const int32_t* ret_incl, int S, int stage, int64_t max_rows, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * fast_oep: lookups in an embedding table sharded over the ranks (rank r owns ids [r * size_per_rank, (r+1) *
+ * size_per_rank)).  ids travel to their owners, table rows travel back.
+ * ref: FastOEP<T>::dispatch / combine (src/fast_oep/all_to_all/fast_oep.cu:52-151), arrangeAndPlanKernel,
+ *      lookupKernel, scatterKernel (src/fast_oep/all_to_all/fast_oep_kernels.cu:15-58,186-245).
+ * Built on the exchange above, created with k = 1, H = embed_dim, hidden_elem_bytes = 0 (no hidden arenas),
+ * scales_dim = 0, S_max = 1 and max_tok * W >= the ids all ranks hold together:
+ *   dispatch  epsb_oep_arrange_plan; epsb_exchange_begin; publish_plans(send_incl, send_incl, 1); recv_plans;
+ *             epsb_exchange_put_ids(EPSB_FLAG_META); epsb_exchange_wait(EPSB_FLAG_META)
+ *   combine   epsb_exchange_lookup_put(EPSB_FLAG_COMBINE(1, 0)); epsb_exchange_wait(same); epsb_oep_scatter from
+ *             the EPSB_ARENA_OUT rows.
+ * epsb_oep_arrange_plan: stable counting sort of the ids by owner (the reference hands out positions with atomics,
+ * so its order inside an owner's block is arbitrary; the looked-up result does not depend on it).  send_incl [W]
+ * inclusive counts per owner, mapping [n]: id i -> its position in the arranged order or -1 (negative ids, and ids
+ * beyond the table, are skipped: their output rows are left untouched), send_map [n]: the inverse.
+ * -------------------------------------------------------------------------- */
+int epsb_oep_arrange_plan(const int32_t* ids, int64_t n, int64_t size_per_rank, int W, int32_t* send_incl,
+                          int32_t* mapping, int32_t* send_map, void* stream);
+int epsb_exchange_put_ids(epsb_exchange_t* x, int flag_slot, const int32_t* ids, const int32_t* send_map,
+                          const int32_t* send_incl, int64_t n, void* stream);
+/* table: this rank's shard [size_per_rank, embed_dim] bf16; row id % size_per_rank answers a received id. */
+int epsb_exchange_lookup_put(epsb_exchange_t* x, int flag_slot, const void* table, int64_t size_per_rank,
+                             int64_t max_rows, void* stream);
+/* out[dst(i), :] = rows[mapping[i], :] for mapping[i] >= 0, dst(i) = i or, with do_permute, the n-gram-major position
+ * i / n_grams + (i % n_grams) * (n / n_grams). */
+int epsb_oep_scatter(const void* rows, const int32_t* mapping, int64_t n, int64_t row_bytes, int64_t n_grams,
+                     int do_permute, void* out, void* stream);
+
+/* ----------------------------------------------------------------------------
+ * TP <-> DP conversion of [tokens, hidden] bf16 rows inside a tensor-parallel
+ * group of the box (the step either side of the MoE block in a model whose
+ * attention is tensor-parallel).
+ * ref: TPDPConvertor (src/communication/tp_dp_convertor.cu:54-129),
+ *      AllGatherRunner (src/communication/allgather_runner.cu:13-83),
+ *      ReduceScatterRunner (src/communication/reducescatter_runner.cu:61-122).
+ * Every rank of the group owns one symmetric region (epsb_symm_alloc) of
+ * epsb_tpdp_region_bytes: buffer_rows x buffer_hidden bf16 (the reference sizes
+ * it attn_tp_size * tp_max_num_tokens rows) followed by flag words.  A call works
+ * on tp_num_tokens rows of `hidden` (<= buffer_hidden) columns; rank r owns rows
+ * [offset_r, offset_r + n_r), n_r = tp_num_tokens / tp_size (+1 for the first
+ * tp_num_tokens % tp_size ranks), the reference's split (tp_dp_convertor.cu:54-62).
+ * regions: host array of tp_size device pointers, entry r = rank r's region as
+ * mapped here.  One collective is four launches on every rank, with `epoch` a
+ * number that grows with every collective of the group:
+ *   all-gather      signal(slot 0) wait(slot 0) all_gather_put(slot 1) wait(slot 1)
+ *   reduce-scatter  signal(slot 2) wait(slot 2) reduce_scatter_sum(slot 3) wait(slot 3)
+ * "ready" (even slot): my buffer holds my input and I no longer read anybody's
+ * previous result; the data kernel releases the odd slot at every peer when its
+ * last CTA is done.  all_gather_put uses peer stores, reduce_scatter_sum peer
+ * loads (fp32 sum in rank order, so every rank would get the same bits).
+ * A wait that runs out of time writes EPSB_TPDP_TIMEOUT + slot into status[0].
+ * -------------------------------------------------------------------------- */
+#define EPSB_TPDP_TIMEOUT 80
+int epsb_tpdp_region_bytes(int64_t buffer_rows, int64_t buffer_hidden, int64_t* bytes);
+int epsb_tpdp_signal(void* const* regions, int tp_rank, int tp_size, int64_t buffer_rows, int64_t buffer_hidden, int slot,
+                     int epoch, void* stream);
+int epsb_tpdp_wait(const void* my_region, int tp_size, int64_t buffer_rows, int64_t buffer_hidden, int slot, int epoch,
+                   int32_t* status, int64_t timeout_ns, void* stream);
+int epsb_tpdp_all_gather_put(void* const* regions, int tp_rank, int tp_size, int64_t buffer_rows, int64_t tp_num_tokens,
+                             int64_t hidden, int64_t buffer_hidden, int slot, int epoch, void* stream);
+int epsb_tpdp_reduce_scatter_sum(void* const* regions, int tp_rank, int tp_size, int64_t buffer_rows,
+                                 int64_t tp_num_tokens, int64_t hidden, int64_t buffer_hidden, int slot, int epoch,
+                                 void* stream);
 
 #ifdef __cplusplus
 }

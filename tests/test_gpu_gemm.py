@@ -208,3 +208,31 @@ def test_gemm_errors(cuda):
     with pytest.raises(EpsError):
         ops.grouped_gemm_fp8(ops.GEMM_PLAIN, A, torch.zeros((4, 1), device=cuda), torch.zeros((1, 128, 100), dtype=torch.uint8, device=cuda),
                              torch.zeros((1, 1, 1), device=cuda), torch.zeros(2, dtype=torch.int32, device=cuda))
+
+
+@pytest.mark.parametrize("rows,N,K", [([200, 17, 0, 129], 512, 256), ([1, 128, 300], 384, 192), ([64] * 8, 1024, 2048),
+                                      ([700], 256, 64)])
+def test_grouped_gemm_bf16_vs_fp32_reference(cuda, rows, N, K):
+    """The bf16 grouped GEMM (the reference's aok_run) against a plain fp32 matmul of the same bf16 operands: fp32
+    accumulation and one rounding on both sides, so the results agree to one bf16 ulp (summation order differs)."""
+    from eps_b200 import ops
+
+    g = torch.Generator().manual_seed(len(rows) * 1000 + N)
+    E, D = len(rows), sum(rows)
+    excl = torch.tensor([0] + list(np.cumsum(rows)), dtype=torch.int32, device=cuda)
+    A = torch.randn((D + 5, K), generator=g).to(torch.bfloat16).to(cuda)
+    B = (torch.randn((E, N, K), generator=g) * 0.05).to(torch.bfloat16).to(cuda)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    out = torch.full((D + 5, N), 7.0, dtype=torch.bfloat16, device=cuda)
+    ops.grouped_gemm_bf16(A, B, excl, out=out, status=status)
+    torch.cuda.synchronize()
+    _check_status(status)
+    ex = excl.cpu().numpy()
+    for e in range(E):
+        a, b = int(ex[e]), int(ex[e + 1])
+        if b == a:
+            continue
+        want = A[a:b].float() @ B[e].float().t()
+        got = out[a:b].float()
+        assert torch.all((got - want).abs() <= 2.0 ** -8 * want.abs() + 1e-3), f"expert {e}"
+    assert torch.all(out[D:] == 7.0)   # rows outside every expert are not touched
