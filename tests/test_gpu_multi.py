@@ -264,7 +264,8 @@ def _native_worker(rank, world, uid, q):
         a2a = FastEP(k2, E2, H2, 256, comm)
         excl2 = torch.empty((EL2 + 1,), dtype=torch.int32, device=dev)
         expert_x = torch.zeros((256 * k2, H2), dtype=torch.bfloat16, device=dev)
-        a2a.dispatch(excl2, expert_x, x2.to(dev), torch.from_numpy(idx2).to(dev), 256)
+        x2_dev = x2.to(dev)   # combine reads the raw tokens again (identity experts): the caller keeps them alive
+        a2a.dispatch(excl2, expert_x, x2_dev, torch.from_numpy(idx2).to(dev), 256)
         ex = excl2.cpu().numpy()
         y = torch.zeros_like(expert_x)
         for le in range(EL2):

@@ -251,7 +251,8 @@ def test_fast_ep_ops_bit_exact(cuda, oracle, eps_pkg):
     a2a = AllToAll(k, E, H, 256, None)
     excl = torch.empty((E + 1,), dtype=torch.int32, device=cuda)
     expert_x = torch.zeros((256 * k, H), dtype=torch.bfloat16, device=cuda)
-    a2a.dispatch(excl, expert_x, x.to(cuda), torch.from_numpy(idx).to(cuda), 256)
+    x_dev = x.to(cuda)   # combine reads the raw tokens again (identity experts): the caller keeps them alive
+    a2a.dispatch(excl, expert_x, x_dev, torch.from_numpy(idx).to(cuda), 256)
     ex = excl.cpu().numpy()
     rexcl, rmap = oracle.fastep_expand_plan(idx, E)
     assert np.array_equal(ex, rexcl)
@@ -318,7 +319,7 @@ def test_communication_ops_world_of_one(cuda, eps_pkg):
     sync_check_cuda_error_eps()
     assert torch.equal(rs.output(), before)    # a group of one: the sum over one rank
     with pytest.raises(RuntimeError, match="should be smaller than or equal to"):
-        tpdp.get_all_gather_context(40, 1024)
+        tpdp.get_all_gather_context(40, 1024).input()
     del tpdp
     with pytest.raises(RuntimeError, match="multi-node"):
         MscclppCommunicator(uid, MscclppCommunicatorParams(0, 2, 1))
