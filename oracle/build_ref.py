@@ -29,6 +29,7 @@ REF_SOURCES = [
     "src/common/debug.cu",
     "src/utils/topk_sigmoid.cu",
     "src/utils/rms_norm.cu",
+    "src/fast_ep/all_to_all/fast_ep_kernels.cu",
 ]
 
 

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include "src/executor/activations.cuh"
+#include "src/fast_ep/all_to_all/fast_ep_kernels.cuh"
 #include "src/quant/fp8.cuh"
 #include "src/scheduler/comm_expander.cuh"
 #include "src/scheduler/gemm_expander.cuh"
@@ -211,6 +212,58 @@ int ref_topk_sigmoid_bf16(const bf16* scores, const float* bias, float* expert_s
 int ref_rms_norm_bf16(bf16* out, const bf16* input, const bf16* scale, float eps, int m, int n) {
   try {
     eps::rms_norm<bf16>(out, input, scale, eps, m, n, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+// fast_ep/all_to_all/fast_ep_kernels.cu:158 (expandPlanKernel<E> for E in {512, 256, 128, 32}, blockExpandPlanKernel else)
+void ref_fastep_expand_plan(const int* idx, int* excl, int* mapping, long long T, long long k, long long E) {
+  fast_ep::ExpandPlan p{T, k, E, idx, excl, mapping};
+  fast_ep::expandPlan(p, 0);
+}
+
+// fast_ep_kernels.cu:202 (cols must be one of the reference's HIDDEN_SIZE_SWITCH values)
+int ref_fastep_expand(const bf16* src, bf16* dst, long long cols, const int* idx, int* excl, int* mapping, long long T,
+                      long long k, long long E) {
+  fast_ep::ExpandParams<bf16> p{src, dst, cols, fast_ep::ExpandPlan{T, k, E, idx, excl, mapping}};
+  try {
+    fast_ep::expand<bf16>(p, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+// fast_ep_kernels.cu:321
+int ref_fastep_reduce(const bf16* src, bf16* dst, const bf16* shared, const bf16* raw, const float* scales,
+                      long long cols, const int* idx, int* excl, int* mapping, long long T, long long k, long long E) {
+  fast_ep::ReduceParams<bf16, float> p{src, dst, shared, raw, scales, cols, fast_ep::ExpandPlan{T, k, E, idx, excl, mapping}};
+  try {
+    fast_ep::reduce<bf16, float>(p, 0);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+// fast_ep_kernels.cu:591.  The channel calls of the all-gather kernel are no-ops here: the caller passes the table
+// `all_gathered` [W][E+1] already filled, and the plan kernels derive everything else from it.
+void ref_fastep_plan(int* all_gathered, long long my_rank, long long W, long long E, int* remote_recv, int* local_send,
+                     int* gemm_plan, int* arr_src, int* arr_rows, int* arr_dst) {
+  eps::CommBuffHost<int> host(0, 0, my_rank, W);
+  fast_ep::AllGatheredPlan p{my_rank, W, W, E, all_gathered, remote_recv, local_send, gemm_plan,
+                             fast_ep::ArrangePlan{arr_src, arr_rows, arr_dst}, eps::CommBuff<int>(host)};
+  fast_ep::allGatherPlan(p, 0);
+}
+
+// fast_ep_kernels.cu:679
+int ref_fastep_arrange(const bf16* src, bf16* dst, long long W, long long E, long long cols, int* arr_src, int* arr_rows,
+                       int* arr_dst, long long num_tokens_hint) {
+  fast_ep::ArrangeParams<bf16> p{W, E, cols, src, dst, fast_ep::ArrangePlan{arr_src, arr_rows, arr_dst}, num_tokens_hint};
+  try {
+    fast_ep::arrange<bf16>(p, 0);
   } catch (...) {
     return 1;
   }

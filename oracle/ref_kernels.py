@@ -157,3 +157,65 @@ def rms_norm(x, scale, eps):
     _sync()
     return out
 
+
+
+# ------------------------------------------------------------------ fast_ep (src/fast_ep/all_to_all/fast_ep_kernels.cu)
+
+def _ll(v):
+    return ctypes.c_longlong(int(v))
+
+
+def fastep_expand_plan(idx, E):
+    """expandPlan: -> (exclusive_sum [E+1], mapping [T*k])."""
+    T, k = idx.shape
+    dev = idx.device
+    excl = _i32(E + 1, dev, 0)
+    mapping = _i32(T * k, dev, -1)
+    lib().ref_fastep_expand_plan(_p(idx), _p(excl), _p(mapping), _ll(T), _ll(k), _ll(E))
+    _sync()
+    return excl, mapping
+
+
+def fastep_expand(x, idx, excl, mapping, E):
+    """expand: rows of x scattered into send order -> [T*k, H] bf16 (H must be a hidden size the reference lists)."""
+    T, k = idx.shape
+    dst = torch.zeros((max(T * k, 1), x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    rc = lib().ref_fastep_expand(_p(x), _p(dst), _ll(x.shape[1]), _p(idx), _p(excl), _p(mapping), _ll(T), _ll(k), _ll(E))
+    if rc:
+        raise RuntimeError("the reference does not instantiate this hidden size")
+    _sync()
+    return dst
+
+
+def fastep_reduce(rows, raw, w, idx, excl, mapping, E, shared=None):
+    """reduce: weighted combine of the k slots per token -> [T, H] bf16."""
+    T, k = idx.shape
+    out = torch.zeros((max(T, 1), rows.shape[1]), dtype=torch.bfloat16, device=rows.device)
+    rc = lib().ref_fastep_reduce(_p(rows), _p(out), _p(shared), _p(raw), _p(w), _ll(rows.shape[1]), _p(idx), _p(excl),
+                                 _p(mapping), _ll(T), _ll(k), _ll(E))
+    if rc:
+        raise RuntimeError("the reference does not instantiate this hidden size")
+    _sync()
+    return out
+
+
+def fastep_plan(all_gathered, my_rank, W, E):
+    """allGatherPlan on a pre-filled table [W, E+1]: -> (remote_recv [W], local_send [W+1], gemm_plan [EL+1],
+    arr_src, arr_rows, arr_dst [EL*W])."""
+    dev = all_gathered.device
+    EL = E // W
+    remote, send, gplan = _i32(W, dev, 0), _i32(W + 1, dev, 0), _i32(EL + 1, dev, 0)
+    src, rows, dst = _i32(EL * W, dev, 0), _i32(EL * W, dev, 0), _i32(EL * W, dev, 0)
+    lib().ref_fastep_plan(_p(all_gathered), _ll(my_rank), _ll(W), _ll(E), _p(remote), _p(send), _p(gplan), _p(src),
+                          _p(rows), _p(dst))
+    _sync()
+    return remote, send, gplan, src, rows, dst
+
+
+def fastep_arrange(src_rows, out_rows, W, E, arr_src, arr_rows, arr_dst, num_tokens_hint):
+    rc = lib().ref_fastep_arrange(_p(src_rows), _p(out_rows), _ll(W), _ll(E), _ll(src_rows.shape[1]), _p(arr_src),
+                                  _p(arr_rows), _p(arr_dst), _ll(num_tokens_hint))
+    if rc:
+        raise RuntimeError("the reference does not instantiate this hidden size")
+    _sync()
+    return out_rows

@@ -1,8 +1,8 @@
 """Records golden vectors from the REFERENCE's own kernels (oracle/_ref/libeps_ref.so) on a GPU.
 
-Run on a B200:  python tests/golden/make_ref_fixtures.py gpurun_out/golden
-then copy the .npz it writes into tests/golden/.  The CPU test tests/test_oracle_golden.py checks
-the oracle against these files, which is the oracle's parity pin.
+Run on a B200:  python tests/golden/make_ref_fixtures.py [OUT_DIR] [--router-only | --fastep-only]
+(OUT_DIR defaults to this directory, tests/golden/).  The CPU test tests/test_oracle_golden.py checks the oracle
+against these files, which is the oracle's parity pin.
 """
 import os
 import sys
@@ -41,6 +41,50 @@ def record_router(out_dir, dev):
                         idx=idx.cpu().numpy(), w=w.cpu().numpy(),
                         scores_bf16=sb.view(torch.int16).numpy().view(np.uint16), idx_bf16=idx_b.cpu().numpy(),
                         w_bf16=w_b.cpu().numpy())
+
+
+# T, k, E, W, n_zero: E in {256, 32, 128} take the reference's per-expert-count kernels, 24 its generic block kernels
+FASTEP_CASES = [(300, 8, 256, 8, 0), (77, 4, 32, 2, 3), (150, 6, 24, 4, 4), (1000, 8, 128, 4, 0)]
+
+
+def record_fastep(out_dir, dev):
+    """fast_ep: expand plan, the plans derived from an all-gathered count table, and the weighted combine, from the
+    reference's own kernels (src/fast_ep/all_to_all/fast_ep_kernels.cu)."""
+    blob = {"cases": np.array(FASTEP_CASES, dtype=np.int64)}
+    H = 2048
+    for ci, (T, k, E, W, nz) in enumerate(FASTEP_CASES):
+        rng = np.random.default_rng(900 + ci)
+        pre = f"c{ci}_"
+        idx, w = random_routing(rng, T, k, E, nz)
+        d_idx = torch.from_numpy(idx).to(dev)
+        excl, mapping = ref.fastep_expand_plan(d_idx, E)
+        blob[pre + "idx"], blob[pre + "w"] = idx, w
+        blob[pre + "excl"], blob[pre + "mapping"] = excl.cpu().numpy(), mapping.cpu().numpy()[:T * k]
+        ag = np.zeros((W, E + 1), dtype=np.int32)
+        for r in range(W):
+            idx_r, _ = random_routing(np.random.default_rng(5000 + 10 * ci + r), max(1, T - 7 * r), k, E, nz)
+            ag[r] = ref.fastep_expand_plan(torch.from_numpy(idx_r).to(dev), E)[0].cpu().numpy()
+        blob[pre + "all_gathered"] = ag
+        for rank in (0, W - 1):
+            plan = ref.fastep_plan(torch.from_numpy(ag).to(dev), rank, W, E)
+            for name, t in zip(("remote_recv", "local_send", "gemm_plan", "arr_src", "arr_rows", "arr_dst"), plan):
+                blob[pre + f"r{rank}_" + name] = t.cpu().numpy()
+        if ci < 3:   # combine on a few rows of a hidden size the reference instantiates
+            g = torch.Generator().manual_seed(ci)
+            x = torch.randn((T, H), generator=g).to(torch.bfloat16)
+            y = torch.randn((T * k, H), generator=g).to(torch.bfloat16)
+            out = ref.fastep_reduce(y.to(dev), x.to(dev), torch.from_numpy(w).to(dev), d_idx, excl, mapping, E)
+            rows = np.sort(np.random.default_rng(ci).choice(T, size=8, replace=False))
+            b = lambda t: t.view(torch.int16).numpy().view(np.uint16)
+            blob[pre + "reduce_rows"] = rows
+            blob[pre + "reduce_x"] = b(x)[rows]
+            blob[pre + "reduce_out"] = b(out.cpu())[rows]
+            # the rows of y the sampled tokens read, by position in the send order
+            m = mapping.cpu().numpy()[:T * k].reshape(T, k)[rows]
+            blob[pre + "reduce_map"] = m
+            ys = b(y)
+            blob[pre + "reduce_y"] = np.stack([[ys[j] if j < 1000000 else np.zeros(H, np.uint16) for j in row] for row in m])
+    np.savez_compressed(os.path.join(out_dir, "ref_fastep.npz"), **blob)
 
 
 def main(out_dir):
@@ -110,13 +154,18 @@ def main(out_dir):
     np.savez_compressed(os.path.join(out_dir, "ref_silu.npz"), gu=gu.view(torch.int16).numpy().view(np.uint16),
                         act=act.cpu().view(torch.int16).numpy().view(np.uint16))
     record_router(out_dir, dev)
+    record_fastep(out_dir, dev)
     print("wrote fixtures to", out_dir, {k: v.shape for k, v in list(blob.items())[:4]})
 
 
 if __name__ == "__main__":
-    out = sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden"
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    out = args[0] if args else os.path.dirname(os.path.abspath(__file__))
     if "--router-only" in sys.argv:      # adds ref_router.npz without re-recording the other files
         os.makedirs(out, exist_ok=True)
         record_router(out, torch.device("cuda:0"))
+    elif "--fastep-only" in sys.argv:    # adds ref_fastep.npz without re-recording the other files
+        os.makedirs(out, exist_ok=True)
+        record_fastep(out, torch.device("cuda:0"))
     else:
         main(out)

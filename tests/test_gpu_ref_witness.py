@@ -124,3 +124,66 @@ def test_reference_reduce_kernels(cuda, oracle, ref):
         ops.global_reduce(recv, glob, got, W, shared=sh, x=x, zero_scale=zs, ref_arith=True)
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("T,k,E,W,nz", [(300, 8, 256, 8, 0), (77, 4, 32, 2, 3), (150, 6, 24, 4, 4), (4096, 8, 128, 4, 0)])
+def test_reference_fastep_kernels(cuda, oracle, ref, T, k, E, W, nz):
+    """fast_ep's own kernels (expandPlan, expand, allGatherPlan's plan kernels, arrange, reduce) from the reference's
+    sources, beside this repository's and the oracle: plans bit for bit (both of the reference's code paths: the
+    per-expert-count instantiations for E in {512, 256, 128, 32} and the generic block kernel), rows bit for bit."""
+    from eps_b200 import ops
+
+    H = 2048    # a hidden size the reference instantiates
+    rng = np.random.default_rng(T + E)
+    idx, w = random_routing(rng, T, k, E, nz)
+    d_idx = torch.from_numpy(idx).to(cuda)
+    # F1: expand plan
+    r_excl, r_map = ref.fastep_expand_plan(d_idx, E)
+    excl, mapping = ops.fastep_expand_plan(d_idx, E)
+    o_excl, o_map = oracle.fastep_expand_plan(idx, E)
+    torch.cuda.synchronize()
+    assert np.array_equal(r_excl.cpu().numpy(), o_excl) and torch.equal(excl, r_excl)
+    assert np.array_equal(r_map.cpu().numpy()[:T * k], o_map) and torch.equal(mapping[:T * k], r_map[:T * k])
+    # F3: expand (scatter into send order)
+    x = torch.randn((T, H), generator=torch.Generator().manual_seed(T)).to(torch.bfloat16).to(cuda)
+    want = ref.fastep_expand(x, d_idx, r_excl, r_map, E)
+    got = torch.zeros_like(want)
+    ops.scatter_rows(x, got, mapping, k, T * k)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # F2: plans from an all-gathered count table (this rank's column-block of every rank's counts)
+    ag = np.zeros((W, E + 1), dtype=np.int32)
+    for r in range(W):
+        idx_r, _ = random_routing(np.random.default_rng(1000 * r + T), T - 7 * r, k, E, nz)
+        ag[r] = oracle.fastep_expand_plan(idx_r, E)[0]
+    d_ag = torch.from_numpy(ag).to(cuda)
+    for rank in (0, W - 1):
+        r_plan = ref.fastep_plan(d_ag.clone(), rank, W, E)
+        m_plan = ops.fastep_plan(d_ag, rank, W, E)
+        o_plan = oracle.fastep_plan(ag, rank, W, E)
+        torch.cuda.synchronize()
+        for name, a, b, c in zip(("remote_recv", "local_send", "gemm_plan", "arr_src", "arr_rows", "arr_dst"), r_plan,
+                                 m_plan, o_plan):
+            n = len(c)
+            assert np.array_equal(a.cpu().numpy()[:n], c), f"reference vs oracle: {name}"
+            assert np.array_equal(b.cpu().numpy()[:n], c), f"this repository vs oracle: {name}"
+    # F3: arrange [source][expert] -> [expert][source] with rank 0's plan
+    _, _, gplan, a_src, a_rows, a_dst = ops.fastep_plan(d_ag, 0, W, E)
+    R = int(gplan[-1])
+    rows_in = torch.randn((R + 3, H), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(cuda)
+    want = torch.zeros((R + 3, H), dtype=torch.bfloat16, device=cuda)
+    ref.fastep_arrange(rows_in, want, W, E, a_src, a_rows, a_dst, R)
+    got = torch.zeros_like(want)
+    ops.arrange_rows(rows_in, got, a_src, a_rows, a_dst, (E // W) * W, R + 3)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # F3: reduce (weighted combine, identity-expert slots read the raw token, optional shared-expert rows)
+    y = torch.randn((T * k, H), generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(cuda)
+    d_w = torch.from_numpy(w).to(cuda)
+    shared = torch.randn((T, H), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(cuda)
+    for sh in (None, shared):
+        want = ref.fastep_reduce(y, x, d_w, d_idx, r_excl, r_map, E, shared=sh)
+        got = torch.zeros((T, H), dtype=torch.bfloat16, device=cuda)
+        ops.fastep_reduce(y, x, d_w, mapping, got, shared=sh)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want[:T])

@@ -86,3 +86,31 @@ def test_router_matches_reference_kernel(oracle):
         assert same.mean() > 0.95
         assert np.allclose(w[same], ref_w[same], rtol=2e-6, atol=0)
 
+
+
+def test_fastep_matches_reference_kernels(oracle):
+    """fast_ep's expand plan, the plans derived from the all-gathered counts and the weighted combine against vectors
+    recorded from the reference's own kernels (both its per-expert-count instantiations and its generic kernels)."""
+    if not os.path.exists(os.path.join(GOLD, "ref_fastep.npz")):
+        pytest.skip("tests/golden/ref_fastep.npz has not been recorded")
+    g = _load("ref_fastep.npz")
+    for ci, (T, k, E, W, nz) in enumerate(g["cases"].tolist()):
+        pre = f"c{ci}_"
+        idx, w = g[pre + "idx"], g[pre + "w"]
+        excl, mapping = oracle.fastep_expand_plan(idx, E)
+        assert np.array_equal(excl, g[pre + "excl"]) and np.array_equal(mapping, g[pre + "mapping"])
+        ag = g[pre + "all_gathered"]
+        for r in range(W):   # the table rows are expand plans too
+            assert ag[r, 0] == 0 and np.all(np.diff(ag[r]) >= 0)
+        for rank in (0, W - 1):
+            plan = oracle.fastep_plan(ag, rank, W, E)
+            for name, mine in zip(("remote_recv", "local_send", "gemm_plan", "arr_src", "arr_rows", "arr_dst"), plan):
+                assert np.array_equal(mine, g[pre + f"r{rank}_" + name][:len(mine)]), (ci, rank, name)
+        if pre + "reduce_rows" in g:
+            rows, m = g[pre + "reduce_rows"], g[pre + "reduce_map"]
+            n, H = len(rows), g[pre + "reduce_x"].shape[1]
+            # the sampled tokens as a little problem of their own: row j of token i sits at position i*k + j
+            ys = g[pre + "reduce_y"].reshape(n * k, H)
+            local_map = np.where(m < 1000000, np.arange(n * k).reshape(n, k), 1000000 + np.arange(n)[:, None])
+            out = oracle.fastep_reduce(ys, g[pre + "reduce_x"], w[rows], local_map.reshape(-1).astype(np.int32))
+            assert np.array_equal(out, g[pre + "reduce_out"])
