@@ -70,6 +70,7 @@ struct SharedStorage {
 };
 
 struct GemmParams {
+  const int32_t* a_rows;  // optional: GEMM row m reads row a_rows[m] of A and a_s (index-driven A loads)
   const float* a_s;
   const float* b_s;
   const int32_t* excl;
@@ -127,7 +128,8 @@ __device__ __forceinline__ bool tail_tile(const GemmParams& p, Storage* sm, cons
   const int tok0 = half * kTh;                           // first token (tile-relative) of this warp
   const bool tok_ok = lane < kTh && tok0 + lane < c.rows_left;
   const int64_t my_row = (int64_t)c.row0 + tok0 + lane;  // the token whose scale this lane carries
-  const float* as_row = p.a_s + (tok_ok ? my_row : (int64_t)c.row0) * KB;
+  const int64_t src_row = tok_ok ? my_row : (int64_t)c.row0;   // row of A / a_s this lane's token comes from
+  const float* as_row = p.a_s + (p.a_rows != nullptr ? (int64_t)__ldg(p.a_rows + src_row) : src_row) * KB;
   int blk0, blk1;
   if (kMode == EPSB_GEMM_GATEUP) {
     blk0 = c.n;
@@ -230,7 +232,20 @@ __device__ __forceinline__ bool tail_tile(const GemmParams& p, Storage* sm, cons
 // tail tiles, which then fill 8 or 4 KB of the stage's A region instead of 16.
 struct AMaps {
   CUtensorMap rows128, rows64, rows32;
+  CUtensorMap row1;   // box of ONE row: the shape tile::gather4 loads take (four such rows per instruction)
 };
+
+// Four rows of A, picked by index, land as four consecutive 128-byte rows of the stage (TMA tile::gather4).  The
+// 128-byte swizzle is a function of the shared-memory address, so 32 such loads fill the A region exactly like
+// one 128-row box load would.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, int x, int r0, int r1, int r2, int r3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
 
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -294,8 +309,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
   static_assert(128 * 40 + 256 * 232 <= kThreads * 168, "setmaxnreg budget exceeds the CTA's register pool");
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 0 && lane == 0) {
-      // ------------------------------------------------ TMA producer
+    if (warp == 0) {
+      // ------------------------------------------------ TMA producer.  Lane 0 waits for the stage, announces the
+      // bytes and loads the weights; the A tile comes either as one box load (lane 0) or, when the caller gave a
+      // row index per GEMM row, as one gather4 per lane (lane j brings tile rows 4j .. 4j+3).
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -308,19 +325,36 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
           brow0 = (int)(c.e * p.N + c.n * kBN);
           brow1 = brow0 + 128;
         }
+        const int a_rows_tile = c.tail ? c.tail : kBM;   // rows of A this tile stages
+        int r4[4] = {0, 0, 0, 0};
+        if (p.a_rows != nullptr) {
+          // rows past the expert's end repeat its first row: loaded, multiplied, never stored
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const int r = 4 * lane + i;
+            r4[i] = __ldg(p.a_rows + c.row0 + (r < c.rows_left ? r : 0));
+          }
+        }
         for (int kb = 0; kb < KB; kb++, it++) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          if (!(ok = mbar_wait(&sm->empty[s], ph ^ 1, sm, p.status, 11))) break;
-          mbar_expect_tx(&sm->full[s], (c.tail ? c.tail * kBK : kABytes) + kBBytes);
+          if (lane == 0) ok = mbar_wait(&sm->empty[s], ph ^ 1, sm, p.status, 11);
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          if (!ok) break;
           uint8_t* base = sm->tiles[s];
-          tma_load_2d(base, c.tail == 0 ? &tmap_a.rows128 : (c.tail == 64 ? &tmap_a.rows64 : &tmap_a.rows32), kb * kBK,
-                      c.row0, &sm->full[s]);
-          tma_load_2d(base + kABytes, &tmap_b, kb * kBK, brow0, &sm->full[s]);
-          tma_load_2d(base + kABytes + kABytes, &tmap_b, kb * kBK, brow1, &sm->full[s]);
+          if (lane == 0) {
+            mbar_expect_tx(&sm->full[s], a_rows_tile * kBK + kBBytes);
+            if (p.a_rows == nullptr)
+              tma_load_2d(base, c.tail == 0 ? &tmap_a.rows128 : (c.tail == 64 ? &tmap_a.rows64 : &tmap_a.rows32), kb * kBK,
+                          c.row0, &sm->full[s]);
+            tma_load_2d(base + kABytes, &tmap_b, kb * kBK, brow0, &sm->full[s]);
+            tma_load_2d(base + kABytes + kABytes, &tmap_b, kb * kBK, brow1, &sm->full[s]);
+          }
+          if (p.a_rows != nullptr && 4 * lane < a_rows_tile)
+            tma_gather4(base + lane * 4 * kBK, &tmap_a.row1, kb * kBK, r4[0], r4[1], r4[2], r4[3], &sm->full[s]);
         }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         // let copies already issued land before the CTA's shared memory is released
         const uint64_t t0 = global_ns();
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -390,7 +424,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
       }
       const int64_t grow = (int64_t)c.row0 + r_in_tile;
       const bool row_ok = r_in_tile < c.rows_left;
-      const float* as_row = p.a_s + (row_ok ? grow : (int64_t)c.row0) * KBs;
+      const int64_t src_row = row_ok ? grow : (int64_t)c.row0;
+      const float* as_row = p.a_s + (p.a_rows != nullptr ? (int64_t)__ldg(p.a_rows + src_row) : src_row) * KBs;
       // the two 128-wide scale blocks this thread's columns belong to
       const float* bs0;
       const float* bs1;
@@ -598,10 +633,12 @@ int launch(const AMaps& ta, const CUtensorMap& tb, const GemmParams& p, int grid
 
 using namespace epsb;
 
-extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
-                                     const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K,
-                                     void* C, float* c_s, const float* row_w, int32_t* status, int sm_count,
-                                     void* stream) {
+// a_rows == nullptr: GEMM row m is row m of A (a_src_rows = max_rows).  Otherwise GEMM row m is row a_rows[m] of the
+// a_src_rows x K matrix A (and of a_s).
+static int grouped_gemm_fp8_impl(int mode, const void* A, const float* a_s, int64_t a_src_rows, const int32_t* a_rows,
+                                 const void* B, const float* b_s, const int32_t* excl, int num_experts, int64_t max_rows,
+                                 int64_t N, int64_t K, void* C, float* c_s, const float* row_w, int32_t* status,
+                                 int sm_count, void* stream) {
   EPSB_REQUIRE(sm_count >= 0, EPSB_ERR_INVALID, "sm_count %d is negative", sm_count);
   EPSB_REQUIRE(mode == EPSB_GEMM_PLAIN || mode == EPSB_GEMM_GATEUP || mode == EPSB_GEMM_DOWN, EPSB_ERR_INVALID,
                "unknown GEMM mode %d", mode);
@@ -613,20 +650,24 @@ extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, 
                "gate/up mode needs N = 2*I with I %% 128 == 0 and an output scale buffer");
   EPSB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 && ((uintptr_t)C & 15) == 0, EPSB_ERR_INVALID,
                "A, B and C must be 16-byte aligned");
-  EPSB_REQUIRE((int64_t)num_experts * N < (1ll << 31) && max_rows < (1ll << 31), EPSB_ERR_INVALID,
-               "tensor too large for 32-bit TMA coordinates");
+  EPSB_REQUIRE((int64_t)num_experts * N < (1ll << 31) && max_rows < (1ll << 31) && a_src_rows < (1ll << 31),
+               EPSB_ERR_INVALID, "tensor too large for 32-bit TMA coordinates");
   if (max_rows <= 0) return EPSB_OK;
+  EPSB_REQUIRE(a_src_rows > 0, EPSB_ERR_INVALID, "the source matrix of A has no rows");
   AMaps ta;
   CUtensorMap tb;
-  int rc = make_map(&ta.rows128, A, max_rows, K, 128);
+  int rc = make_map(&ta.rows128, A, a_src_rows, K, 128);
   if (rc) return rc;
-  rc = make_map(&ta.rows64, A, max_rows, K, 64);
+  rc = make_map(&ta.rows64, A, a_src_rows, K, 64);
   if (rc) return rc;
-  rc = make_map(&ta.rows32, A, max_rows, K, 32);
+  rc = make_map(&ta.rows32, A, a_src_rows, K, 32);
+  if (rc) return rc;
+  rc = make_map(&ta.row1, A, a_src_rows, K, 1);
   if (rc) return rc;
   rc = make_map(&tb, B, (int64_t)num_experts * N, K);
   if (rc) return rc;
   GemmParams p;
+  p.a_rows = a_rows;
   p.a_s = a_s;
   p.b_s = b_s;
   p.excl = excl;
@@ -649,4 +690,21 @@ extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, 
     case EPSB_GEMM_DOWN: return launch<EPSB_GEMM_DOWN>(ta, tb, p, (int)grid, st);
     default: return launch<EPSB_GEMM_PLAIN>(ta, tb, p, (int)grid, st);
   }
+}
+
+extern "C" int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
+                                     const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K,
+                                     void* C, float* c_s, const float* row_w, int32_t* status, int sm_count,
+                                     void* stream) {
+  return grouped_gemm_fp8_impl(mode, A, a_s, max_rows, nullptr, B, b_s, excl, num_experts, max_rows, N, K, C, c_s, row_w,
+                               status, sm_count, stream);
+}
+
+extern "C" int epsb_grouped_gemm_fp8_gather(int mode, const void* A_src, const float* a_s_src, int64_t a_src_rows,
+                                            const int32_t* a_rows, const void* B, const float* b_s, const int32_t* excl,
+                                            int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C, float* c_s,
+                                            const float* row_w, int32_t* status, int sm_count, void* stream) {
+  EPSB_REQUIRE(a_rows != nullptr, EPSB_ERR_INVALID, "a_rows is NULL: use epsb_grouped_gemm_fp8");
+  return grouped_gemm_fp8_impl(mode, A_src, a_s_src, a_src_rows, a_rows, B, b_s, excl, num_experts, max_rows, N, K, C,
+                               c_s, row_w, status, sm_count, stream);
 }

@@ -132,6 +132,24 @@ oep_scatter_kernel(const uint8_t* __restrict__ rows, const int32_t* __restrict__
   }
 }
 
+// Per GEMM row d < excl[EL]: where its input row comes from and what it is worth.  gemm_map[d] = received row * k +
+// slot.  a_rows[d] = the received row, or, when send_map is given (a world of one, where the receive order is the send
+// order), the token behind it: send_map[row] % T.  row_w[d] = w_src[a_rows[d] * k + slot].
+__global__ void __launch_bounds__(256)
+gemm_row_sources_kernel(const int32_t* __restrict__ gemm_map, const int32_t* __restrict__ excl, int num_experts, int k,
+                        const int32_t* __restrict__ send_map, int T, const float* __restrict__ w_src,
+                        int32_t* __restrict__ a_rows, float* __restrict__ row_w) {
+  const int64_t D = excl[num_experts];
+  for (int64_t d = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; d < D; d += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t m = gemm_map[d];
+    int32_t row = m / k;
+    const int slot = m - row * k;
+    if (send_map != nullptr) row = send_map[row] % T;
+    a_rows[d] = row;
+    if (row_w != nullptr) row_w[d] = w_src[(int64_t)row * k + slot];
+  }
+}
+
 int move_grid(int64_t rows) {
   int64_t want = (rows + kMoveWarps - 1) / kMoveWarps;
   const int64_t cap = (int64_t)sm_count() * 8;
@@ -210,6 +228,20 @@ extern "C" int epsb_arrange_rows(const void* src, void* dst, const int32_t* src_
   arrange_rows_kernel<<<move_grid(max_rows), kMoveThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint8_t*)src, (uint8_t*)dst, src_off, rows, dst_off, n_seg, row_bytes);
   return check_launch("arrange_rows");
+}
+
+extern "C" int epsb_gemm_row_sources(const int32_t* gemm_map, const int32_t* excl, int num_experts, int k,
+                                     const int32_t* send_map, int T, const float* w_src, int64_t max_rows,
+                                     int32_t* a_rows, float* row_w, void* stream) {
+  EPSB_REQUIRE(k > 0 && num_experts > 0 && (send_map == nullptr || T > 0) && a_rows != nullptr, EPSB_ERR_INVALID,
+               "bad arguments k=%d num_experts=%d T=%d", k, num_experts, T);
+  EPSB_REQUIRE(row_w == nullptr || w_src != nullptr, EPSB_ERR_INVALID, "row_w needs w_src");
+  if (max_rows <= 0) return EPSB_OK;
+  int64_t blocks = (max_rows + 255) / 256;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+  gemm_row_sources_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(gemm_map, excl, num_experts, k,
+                                                                                      send_map, T, w_src, a_rows, row_w);
+  return check_launch("gemm_row_sources");
 }
 
 extern "C" int epsb_gather_row_weights(const float* w_recv, const int32_t* gemm_map, const int32_t* excl,

@@ -49,6 +49,13 @@ class MoELayerFP8:
         self.max_gemm_rows = min(worst, max_gemm_rows) if max_gemm_rows is not None else worst
         D = max(self.max_gemm_rows, 1)
         dev = self.dev
+        # With the device-side exchange (and in a world of one) every GEMM row knows its source row (the arena, or the
+        # caller's own quantised tokens): ONE gather brings the rows into expert order, nothing is staged for sending.
+        self.direct_sources = self.W == 1 or self.sched.peer is not None
+        # True: the gate/up GEMM fetches those rows itself (TMA gather4 in its producer) and the gather pass goes too.
+        # Measured on cfg1 this is slower (32 four-row loads per stage instead of one box load: 3.4 vs 2.1 ms), so it is
+        # off; small-row workloads may set it.
+        self.gemm_gathers_rows = False
         self.A = torch.empty((D, hidden), dtype=torch.uint8, device=dev)
         self.A_s = torch.empty((D, hidden // 128), dtype=torch.float32, device=dev)
         self.act = torch.empty((D, inter), dtype=torch.uint8, device=dev)
@@ -109,11 +116,19 @@ class MoELayerFP8:
         if rows_k > self.max_gemm_rows:
             raise EpsError(f"{rows_k} possible GEMM rows exceed max_gemm_rows {self.max_gemm_rows}")
         D = max(rows_k, 1)
-        sched.prologue(expert_weights, xq, xs, self.A_s[:D], raw_input=x, defer_exchange=True)
-        # NCCL transport / world of one: gate weights, hidden rows, scales to send order; scales to GEMM order;
-        # GEMM-row gate weights.  Device-side exchange: nothing is staged, only the GEMM-row gate weights.
-        n += 1 if sched.peer is not None else 5
-        row_w = sched.gemm_row_weights() if self.W == 1 else None
+        a_rows = src_h = src_s = None
+        if self.W == 1:
+            # nothing is staged: the GEMM reads the quantised tokens through the composed plans
+            sched.context.raw_input = x
+            a_rows, row_w, src_h, src_s = sched.gemm_sources(expert_weights, xq, xs)
+            n += 1
+        else:
+            sched.prologue(expert_weights, xq, xs, None if self.direct_sources else self.A_s[:D], raw_input=x,
+                           defer_exchange=True)
+            # NCCL transport: gate weights, hidden rows, scales to send order; scales to GEMM order; GEMM-row gate
+            # weights.  Device-side exchange: nothing is staged, only the per-GEMM-row sources.
+            n += 1 if self.direct_sources else 5
+            row_w = None
         eps_ = EL // S
 
         def stage_gemms(s):
@@ -121,9 +136,18 @@ class MoELayerFP8:
             ev = self.gateup_events if s == 0 else None
             if ev is not None:
                 ev[0].record()
-            ops.grouped_gemm_fp8(ops.GEMM_GATEUP, self.A[:D], self.A_s[:D], self.wgu[s * eps_:(s + 1) * eps_],
-                                 self.wgu_s[s * eps_:(s + 1) * eps_], ex, out=self.act[:D], out_scales=self.act_s[:D],
-                                 status=self.status)
+            if self.direct_sources and self.gemm_gathers_rows:
+                ops.grouped_gemm_fp8(ops.GEMM_GATEUP, src_h, src_s, self.wgu[s * eps_:(s + 1) * eps_],
+                                     self.wgu_s[s * eps_:(s + 1) * eps_], ex, out=self.act[:D],
+                                     out_scales=self.act_s[:D], status=self.status, a_rows=a_rows[:D])
+            else:
+                if self.direct_sources:   # one gather from the source rows into expert order (rows and their scales)
+                    b0, b1 = s * eps_, (s + 1) * eps_
+                    ops.gather_rows(src_h, self.A[:D], a_rows, 1, ops.INT32_MAX, bounds=excl, b0=b0, b1=b1)
+                    ops.gather_rows(src_s, self.A_s[:D], a_rows, 1, ops.INT32_MAX, bounds=excl, b0=b0, b1=b1)
+                ops.grouped_gemm_fp8(ops.GEMM_GATEUP, self.A[:D], self.A_s[:D], self.wgu[s * eps_:(s + 1) * eps_],
+                                     self.wgu_s[s * eps_:(s + 1) * eps_], ex, out=self.act[:D],
+                                     out_scales=self.act_s[:D], status=self.status)
             if ev is not None:
                 ev[1].record()
             ops.grouped_gemm_fp8(ops.GEMM_DOWN, self.act[:D], self.act_s[:D], self.wd[s * eps_:(s + 1) * eps_],
@@ -132,9 +156,8 @@ class MoELayerFP8:
 
         if self.W == 1:
             for s in range(S):
-                sched.gemm_expand(self.A[:D], s)
                 stage_gemms(s)
-                n += 3
+                n += 2 if self.gemm_gathers_rows else 4
         else:
             # Stage pipeline on two streams (the reference leaves this to its caller): all dispatches are queued on
             # the communication stream up front, each combine as soon as its stage has been reduced, so the exchange
@@ -155,9 +178,13 @@ class MoELayerFP8:
             for s in range(S):
                 main.wait_event(disp_done[s])
                 if s == 0:  # the first dispatch carried the gate weights and the input scales
-                    sched.finish_prologue()
-                    row_w = sched.gemm_row_weights()
-                sched.gemm_expand(self.A[:D], s)
+                    if self.direct_sources:
+                        a_rows, row_w, src_h, src_s = sched.gemm_sources(expert_weights, xq, xs)
+                    else:
+                        sched.finish_prologue()
+                        row_w = sched.gemm_row_weights()
+                if not self.direct_sources:
+                    sched.gemm_expand(self.A[:D], s)
                 stage_gemms(s)
                 mark_lr = self._exchange_mark("combine", s, main) if sched.peer is not None else None
                 sched.local_reduce(self.Y[:D], s, pre_weighted=True)   # device-side exchange: reduce + store at the source
@@ -168,7 +195,7 @@ class MoELayerFP8:
                     mark = self._exchange_mark("combine", s, comm_stream) if sched.peer is None else None
                     sched.combine(s)
                     self._exchange_done(mark, comm_stream)
-                n += 5 if sched.peer is not None else 4
+                n += 4 if (self.gemm_gathers_rows or not self.direct_sources) else 6
             all_back = torch.cuda.Event()
             all_back.record(comm_stream)
         shared_out = self._shared_expert(xq, xs, T) if self.W > 1 else shared_out

@@ -299,9 +299,22 @@ def rms_norm(input, scale, eps, out=None):
     return out
 
 
+def gemm_row_sources(gemm_map, excl, num_experts, k, max_rows, w_src=None, send_map=None, T=0):
+    """-> (a_rows int32 [max_rows], row_w fp32 [max_rows] or None): source row and gate weight of every GEMM row."""
+    dev = gemm_map.device
+    a_rows = torch.empty((max(max_rows, 1),), dtype=torch.int32, device=dev)
+    row_w = torch.empty((max(max_rows, 1),), dtype=torch.float32, device=dev) if w_src is not None else None
+    call("epsb_gemm_row_sources", ptr(gemm_map), ptr(excl), num_experts, k, ptr(send_map), int(T), ptr(w_src), max_rows,
+         ptr(a_rows), ptr(row_w), stream_ptr())
+    return a_rows, row_w
+
+
 def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
-                     tile_tokens=0, sm_count=0):
+                     tile_tokens=0, sm_count=0, a_rows=None):
     """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.
+
+    a_rows: optional int32 [rows]; GEMM row m then reads row a_rows[m] of A / a_s (index-driven A loads), and the
+    outputs have a_rows.numel() rows.
 
     sm_count: SMs this launch may occupy (0 = all), the sm_count of the reference's aok_create.
     tile_tokens > 0 selects the token-N kernel (weights on the MMA's M, that many tokens per tile on N);
@@ -311,7 +324,8 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
     _check(B, "B", _FP8, 3)
     _check(b_s, "B_scale", torch.float32, 3)
     _check(excl, "exclusive_sum", torch.int32, 1)
-    max_rows, K = A.shape
+    src_rows, K = A.shape
+    max_rows = src_rows if a_rows is None else a_rows.numel()
     E, N, K2 = B.shape
     if K2 != K:
         raise EpsError(f"A has K={K} but B has K={K2}")
@@ -329,6 +343,11 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
         call("epsb_grouped_gemm_fp8_tn", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K,
              ptr(C), ptr(row_w), ptr(status), int(tile_tokens), int(sm_count), stream_ptr())
         return C
+    if a_rows is not None:
+        _check(a_rows, "a_rows", torch.int32, 1)
+        call("epsb_grouped_gemm_fp8_gather", mode, ptr(A), ptr(a_s), src_rows, ptr(a_rows), ptr(B), ptr(b_s), ptr(excl),
+             E, max_rows, N, K, ptr(C), ptr(c_s), ptr(row_w), ptr(status), int(sm_count), stream_ptr())
+        return (C, c_s) if mode == GEMM_GATEUP else C
     call("epsb_grouped_gemm_fp8", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K, ptr(C),
          ptr(c_s), ptr(row_w), ptr(status), int(sm_count), stream_ptr())
     return (C, c_s) if mode == GEMM_GATEUP else C

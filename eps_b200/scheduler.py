@@ -384,8 +384,9 @@ class Scheduler:
             h = hidden_states.view(torch.uint8) if hidden_states.dtype == torch.float8_e4m3fn else hidden_states
             if h.dtype != self.hidden_dtype:
                 raise EpsError(f"hidden_states must have dtype {self.hidden_dtype}, got {h.dtype}")
-            if ctx.input_quanted and (input_scales is None or recv_input_scales is None or self.scales_dim == 0):
-                raise EpsError("input_quanted needs input_scales, recv_input_scales and input_scales_dim > 0")
+            if ctx.input_quanted and (input_scales is None or self.scales_dim == 0):
+                raise EpsError("input_quanted needs input_scales and input_scales_dim > 0")
+            # recv_input_scales may be None: a GEMM with index-driven A loads reads the scales where they arrive
             ctx.src_hidden, ctx.src_scales = h, (input_scales if ctx.input_quanted else None)
             ctx.src_idx_w = None
             ctx.scales_out = recv_input_scales if ctx.input_quanted else None
@@ -495,6 +496,22 @@ class Scheduler:
         zero = ctx.zero_scale if (x is not None and x.dtype == torch.bfloat16) else None
         ops.reduce_ep1(gemm_output, ctx.red_map, ctx.glob_map, ctx.ret_incl, ctx.num_stages, self.top_k, output,
                        shared=shared, x=x if zero is not None else None, zero_scale=zero)
+
+    def gemm_sources(self, expert_scales: torch.Tensor, hidden: torch.Tensor, scales: torch.Tensor | None):
+        """For GEMMs with index-driven A loads (no expandForGemm pass): -> (a_rows int32 [GEMM rows], row_w fp32,
+        source rows, source scales).  GEMM row d reads row a_rows[d] of the source: the receive arena, or in a world of
+        one the caller's own `hidden` / `scales` (the receive order is the send order there, so nothing is staged at
+        all).  row_w[d] is the row's gate weight."""
+        ctx = self.context
+        EL, k = self.local_num_experts, self.top_k
+        n = max(ctx.rows_bound, 0) * min(k, EL)
+        if self.W == 1:
+            T = ctx.num_tokens
+            a_rows, row_w = ops.gemm_row_sources(ctx.gemm_map, ctx.excl, EL, k, n, w_src=expert_scales,
+                                                 send_map=ctx.send_map if T > 0 else None, T=T)
+            return a_rows, row_w, hidden, scales
+        a_rows, row_w = ops.gemm_row_sources(ctx.gemm_map, ctx.excl, EL, k, n, w_src=self.recv_w)
+        return a_rows, row_w, self.recv_hidden, self.recv_scales
 
     # helper used by the fused layer
     def gemm_row_weights(self) -> torch.Tensor:

@@ -326,6 +326,23 @@ int epsb_grouped_gemm_fp8(int mode, const void* A, const float* a_s, const void*
                           const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
                           float* c_s, const float* row_w, int32_t* status, int sm_count, void* stream);
 
+/* The same product with index-driven A loads: GEMM row m is row a_rows[m] of the a_src_rows x K matrix A_src (and of
+ * a_s_src), fetched by the kernel's TMA producer four rows at a time (tile::gather4).  This replaces the separate
+ * gather pass into an expert-contiguous A buffer (ref: expandForGemm, src/scheduler/gemm_expander.cu:81-163): the
+ * rows are read where they arrived (or, in a world of one, where the quantiser wrote them).  a_rows [max_rows] int32
+ * on the device (epsb_gemm_row_sources writes it); every other argument as in epsb_grouped_gemm_fp8. */
+int epsb_grouped_gemm_fp8_gather(int mode, const void* A_src, const float* a_s_src, int64_t a_src_rows,
+                                 const int32_t* a_rows, const void* B, const float* b_s, const int32_t* excl,
+                                 int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C, float* c_s,
+                                 const float* row_w, int32_t* status, int sm_count, void* stream);
+
+/* Source row and gate weight of every GEMM row d < excl[num_experts], from the GEMM plan (gemm_map[d] = received row *
+ * k + slot): a_rows[d] = the received row, or with send_map (a world of one: the receive order is the send order) the
+ * token behind it, send_map[row] % T; row_w[d] = w_src[a_rows[d] * k + slot] (NULL to skip).  w_src is the received
+ * gate weights [R, k], or in a world of one the caller's expert_scales [T, k]. */
+int epsb_gemm_row_sources(const int32_t* gemm_map, const int32_t* excl, int num_experts, int k, const int32_t* send_map,
+                          int T, const float* w_src, int64_t max_rows, int32_t* a_rows, float* row_w, void* stream);
+
 /* The same product with the operand roles swapped ("token-N"): 128 weight rows
  * are the MMA's M and an expert's tokens its N, so an expert of up to
  * tile_tokens rows streams its weights exactly once, whatever its row count

@@ -62,8 +62,16 @@ def test_executor_classes(cuda, oracle):
     want = oracle.grouped_gemm_fp8(A, a_s, wq, w_s, excl)
     rms = np.sqrt(np.mean(want ** 2))
     assert np.max(np.abs(C.float().cpu().numpy() - want)) <= 2e-2 * rms
-    with pytest.raises(EpsError, match="FP8 block-scaled"):
+    # without B_scale the reference's bf16 x bf16 GEMM runs: e4m3 codes are the wrong operands for it
+    with pytest.raises(EpsError, match="must have dtype torch.bfloat16"):
         gemm.run(dv(A), dv(wq), None, dv(excl), 0)
+    Ab = torch.from_numpy(oracle.bf16_to_f32(a)).to(torch.bfloat16).to(cuda)
+    Bb = (torch.randn((E, N, K), generator=torch.Generator().manual_seed(1)) * 0.05).to(torch.bfloat16).to(cuda)
+    Cb = gemm.run(Ab, Bb, None, dv(excl), int(excl[-1]))
+    for e in range(E):
+        lo, hi = int(excl[e]), int(excl[e + 1])
+        want_b = Ab[lo:hi].float() @ Bb[e].float().t()
+        assert torch.all((Cb[lo:hi].float() - want_b).abs() <= 2.0 ** -8 * want_b.abs() + 1e-3)
     gu = C  # [rows, 256] bf16 -> act [rows, 128]
     act = silu(gu, dv(excl), int(excl[-1]))
     g, u = gu[:, :128].float(), gu[:, 128:].float()

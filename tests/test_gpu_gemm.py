@@ -236,3 +236,37 @@ def test_grouped_gemm_bf16_vs_fp32_reference(cuda, rows, N, K):
         got = out[a:b].float()
         assert torch.all((got - want).abs() <= 2.0 ** -8 * want.abs() + 1e-3), f"expert {e}"
     assert torch.all(out[D:] == 7.0)   # rows outside every expert are not touched
+
+
+@pytest.mark.parametrize("mode", ["plain", "gateup", "down"])
+@pytest.mark.parametrize("rows", [[128], [130, 0, 7, 33, 64, 65, 200], [64] * 5 + [129, 1, 257]])
+def test_gemm_index_driven_a_loads_equal_a_gathered_copy(cuda, oracle, rows, mode):
+    """GEMM row m read through a_rows[m] from a source matrix (TMA gather4 in the kernel) gives bit for bit what the
+    same kernel gives on a pre-gathered copy of those rows; rows may repeat (a token routed to several experts)."""
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(len(rows) * 7 + len(mode))
+    N, K = (512, 384) if mode != "gateup" else (512, 256)
+    E, D = len(rows), int(sum(rows))
+    excl = np.zeros(E + 1, dtype=np.int32)
+    excl[1:] = np.cumsum(rows)
+    S = 97                                                   # source rows: fewer than GEMM rows, so they repeat
+    src = oracle.bf16_bits(rng.standard_normal((S, K)).astype(np.float32))
+    A_src, as_src = oracle.quant_1x128(src)
+    a_rows = rng.integers(0, S, size=D + 3).astype(np.int32)
+    w = oracle.bf16_to_f32(oracle.bf16_bits((rng.standard_normal((E, N, K)) * 0.02).astype(np.float32)))
+    B, b_s = oracle.quant_block128(w)
+    d = lambda t: _dev(t, cuda)
+    m = {"plain": ops.GEMM_PLAIN, "gateup": ops.GEMM_GATEUP, "down": ops.GEMM_DOWN}[mode]
+    row_w = d(rng.random(D + 3).astype(np.float32)) if mode == "down" else None
+    status = torch.zeros(4, dtype=torch.int32, device=cuda)
+    got = ops.grouped_gemm_fp8(m, d(A_src), d(as_src), d(B), d(b_s), d(excl), row_w=row_w, status=status,
+                               a_rows=d(a_rows))
+    want = ops.grouped_gemm_fp8(m, d(A_src[a_rows]), d(as_src[a_rows]), d(B), d(b_s), d(excl), row_w=row_w,
+                                status=status)
+    torch.cuda.synchronize()
+    _check_status(status)
+    if mode == "gateup":
+        assert torch.equal(got[0][:D], want[0][:D]) and torch.equal(got[1][:D], want[1][:D])
+    else:
+        assert torch.equal(got[:D], want[:D])
