@@ -41,7 +41,6 @@ SIGNATURES = {
     "epsb_fastep_reduce": [_P, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "epsb_silu_run": [_P, _P, _P, _I, _L, _L, _P],
     "epsb_grouped_gemm_fp8": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _P, _I, _P],
-    "epsb_grouped_gemm_fp8_tn": [_I, _P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _I, _I, _P],
     "epsb_rms_norm": [_P, _P, _P, c_float, _L, _L, _P],
     "epsb_router_topk_sigmoid": [_P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],

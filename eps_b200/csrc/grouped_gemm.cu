@@ -60,7 +60,6 @@ struct SharedStorage {
   uint8_t out_stage[2][kBM][kOutRowBytes];  // [column half][row]: tile output on its way to global memory
   uint64_t full[kStages];
   uint64_t empty[kStages];
-  uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t amax_bar;
   uint32_t tmem_base;
@@ -151,7 +150,7 @@ __device__ __forceinline__ bool tail_tile(const GemmParams& p, Storage* sm, cons
       sb0 = __ldg(bs0 + kb + 1);
       sb1 = __ldg(bs1 + kb + 1);
     }
-    bool good = mbar_wait(&sm->tmem_full[it & 1u], (it >> 1) & 1u, sm, p.status, 33);
+    bool good = mbar_wait(&sm->empty[it % Storage::kStages], (it / Storage::kStages) & 1u, sm, p.status, 33);
     good = __all_sync(0xffffffffu, good);
     if (!good) return false;
     tc_fence_after();
@@ -265,7 +264,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
       mbar_init(&sm->empty[s], 1);
     }
     for (int b = 0; b < 2; b++) {
-      mbar_init(&sm->tmem_full[b], 1);
       mbar_init(&sm->tmem_empty[b], 8);  // one arrival per epilogue warp
     }
     mbar_init(&sm->amax_bar, 256);
@@ -398,8 +396,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
               umma_f8(d + (uint32_t)tail, dw1 + 2 * k4, da + 2 * k4, idesc_tail, k4 > 0 ? 1u : 0u);
             }
           }
-          umma_commit(&sm->empty[s]);       // stage reusable once these MMAs have read it
-          umma_commit(&sm->tmem_full[buf]); // accumulator buffer ready for the epilogue
+          // ONE commit per K step: when these MMAs have completed the stage may be refilled (the producer waits on
+          // this barrier) and the accumulator buffer is ready (the epilogue warps wait on the same barrier)
+          umma_commit(&sm->empty[s]);
         }
       }
     }
@@ -448,7 +447,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ AMaps tmap_a, const __grid_const
       };
       auto tmem_of = [&](uint32_t k_it) -> uint32_t { return lane_addr + (k_it & 1u) * (uint32_t)kBN; };
       auto wait_full = [&](uint32_t k_it) -> bool {
-        bool good = mbar_wait(&sm->tmem_full[k_it & 1u], (k_it >> 1) & 1u, sm, p.status, 31);
+        bool good = mbar_wait(&sm->empty[k_it % kStages], (k_it / kStages) & 1u, sm, p.status, 31);
         good = __all_sync(0xffffffffu, good);
         if (good) tc_fence_after();
         return good;

@@ -1,11 +1,11 @@
 """Timing of the FP8 grouped GEMM alone, at benchmark shapes.
 
-  python -m eps_b200.gemm_bench [--mode down|plain|gateup] [--experts 256] [--rows 128] [--jitter 0]
-                                [--N 7168] [--K 2048] [--tile 0] [--iters 10]
+  python -m eps_b200.gemm_bench [--mode down|plain|gateup|bf16] [--experts 256] [--rows 128] [--jitter 0]
+                                [--N 7168] [--K 2048] [--iters 10]
 
 --rows is the mean row count per expert, --jitter the standard deviation of a seeded normal spread around it
-(the routed layer at 4096 tokens, top-8, 256 experts has 128 +- 11).  --tile 0 runs the 128x256 kernel, a
-multiple of 16 runs the token-N kernel with that many tokens per tile.  Prints one JSON line: CUDA-event time
+(the routed layer at 4096 tokens, top-8, 256 experts has 128 +- 11).  --mode bf16 times the bf16 x bf16 grouped
+GEMM (the reference's aok_run), the others the FP8 block-scaled one.  Prints one JSON line: CUDA-event time
 per launch, weight bytes per second and FLOP/s.  This is the command the ncu summaries of the GEMM kernels
 were taken from.
 """
@@ -18,7 +18,7 @@ import torch
 
 from . import ops
 
-MODES = {"plain": ops.GEMM_PLAIN, "gateup": ops.GEMM_GATEUP, "down": ops.GEMM_DOWN}
+MODES = {"plain": ops.GEMM_PLAIN, "gateup": ops.GEMM_GATEUP, "down": ops.GEMM_DOWN, "bf16": -1}
 
 
 def make_problem(experts, rows, jitter, N, K, dev, seed=1):
@@ -36,9 +36,12 @@ def make_problem(experts, rows, jitter, N, K, dev, seed=1):
     return D, excl, A, a_s, B, b_s
 
 
-def run(mode, experts, rows, jitter, N, K, tile, iters):
+def run(mode, experts, rows, jitter, N, K, iters):
     dev = torch.device("cuda")
     D, excl, A, a_s, B, b_s = make_problem(experts, rows, jitter, N, K, dev)
+    if mode == -1:
+        A = torch.randn((D, K), device=dev).to(torch.bfloat16)
+        B = (torch.randn((experts, N, K), device=dev) * 0.05).to(torch.bfloat16)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     if mode == ops.GEMM_GATEUP:
         out = torch.empty((D, N // 2), dtype=torch.uint8, device=dev)
@@ -49,8 +52,10 @@ def run(mode, experts, rows, jitter, N, K, tile, iters):
     row_w = torch.rand(D, device=dev) if mode == ops.GEMM_DOWN else None
 
     def launch():
-        ops.grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=out, out_scales=outs, row_w=row_w, status=status,
-                             tile_tokens=tile)
+        if mode == -1:
+            ops.grouped_gemm_bf16(A, B, excl, out=out, status=status)
+        else:
+            ops.grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=out, out_scales=outs, row_w=row_w, status=status)
 
     for _ in range(3):
         launch()
@@ -65,9 +70,10 @@ def run(mode, experts, rows, jitter, N, K, tile, iters):
     st = status.tolist()
     if st[0] != 0:
         raise RuntimeError(f"bounded wait expired in the GEMM kernel: code {st[0]} on CTA {st[1]}")
-    return {"kernel": "grouped_gemm_fp8" + ("_tn" if tile else ""), "experts": experts, "rows_total": D,
-            "rows_mean": rows, "rows_sd": jitter, "N": N, "K": K, "tile_tokens": tile, "ms": round(ms, 4),
-            "weight_GBps": round(experts * N * K / ms / 1e6, 1), "TFLOPs": round(2.0 * D * N * K / ms / 1e9, 1)}
+    return {"kernel": "grouped_gemm_bf16" if mode == -1 else "grouped_gemm_fp8", "experts": experts, "rows_total": D,
+            "rows_mean": rows, "rows_sd": jitter, "N": N, "K": K, "ms": round(ms, 4),
+            "weight_GBps": round(experts * N * K * (2 if mode == -1 else 1) / ms / 1e6, 1),
+            "TFLOPs": round(2.0 * D * N * K / ms / 1e9, 1)}
 
 
 def main():
@@ -78,10 +84,9 @@ def main():
     ap.add_argument("--jitter", type=float, default=0.0)
     ap.add_argument("--N", type=int, default=7168)
     ap.add_argument("--K", type=int, default=2048)
-    ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
-    print(json.dumps(run(MODES[a.mode], a.experts, a.rows, a.jitter, a.N, a.K, a.tile, a.iters)))
+    print(json.dumps(run(MODES[a.mode], a.experts, a.rows, a.jitter, a.N, a.K, a.iters)))
 
 
 if __name__ == "__main__":

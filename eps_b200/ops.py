@@ -310,15 +310,14 @@ def gemm_row_sources(gemm_map, excl, num_experts, k, max_rows, w_src=None, send_
 
 
 def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_w=None, status=None,
-                     tile_tokens=0, sm_count=0, a_rows=None):
+                     sm_count=0, a_rows=None):
     """FP8 block-scaled grouped GEMM; see include/eps_b200.h for the three modes.
 
     a_rows: optional int32 [rows]; GEMM row m then reads row a_rows[m] of A / a_s (index-driven A loads), and the
     outputs have a_rows.numel() rows.
 
     sm_count: SMs this launch may occupy (0 = all), the sm_count of the reference's aok_create.
-    tile_tokens > 0 selects the token-N kernel (weights on the MMA's M, that many tokens per tile on N);
-    it exists for modes PLAIN and DOWN."""
+    """
     _check(A, "A", _FP8, 2)
     _check(a_s, "A_scale", torch.float32, 2)
     _check(B, "B", _FP8, 3)
@@ -339,10 +338,6 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
     else:
         C = out if out is not None else torch.empty((max_rows, N), dtype=torch.bfloat16, device=dev)
         c_s = None
-    if tile_tokens:
-        call("epsb_grouped_gemm_fp8_tn", mode, ptr(A), ptr(a_s), ptr(B), ptr(b_s), ptr(excl), E, max_rows, N, K,
-             ptr(C), ptr(row_w), ptr(status), int(tile_tokens), int(sm_count), stream_ptr())
-        return C
     if a_rows is not None:
         _check(a_rows, "a_rows", torch.int32, 1)
         call("epsb_grouped_gemm_fp8_gather", mode, ptr(A), ptr(a_s), src_rows, ptr(a_rows), ptr(B), ptr(b_s), ptr(excl),

@@ -343,18 +343,6 @@ int epsb_grouped_gemm_fp8_gather(int mode, const void* A_src, const float* a_s_s
 int epsb_gemm_row_sources(const int32_t* gemm_map, const int32_t* excl, int num_experts, int k, const int32_t* send_map,
                           int T, const float* w_src, int64_t max_rows, int32_t* a_rows, float* row_w, void* stream);
 
-/* The same product with the operand roles swapped ("token-N"): 128 weight rows
- * are the MMA's M and an expert's tokens its N, so an expert of up to
- * tile_tokens rows streams its weights exactly once, whatever its row count
- * (the reference's H20 configuration makes the same swap,
- * src/gemm/aok_grouped_gemm/src/operations/hopper_grouped_gemm.cu:147-170).
- * Arguments as epsb_grouped_gemm_fp8; modes EPSB_GEMM_PLAIN and EPSB_GEMM_DOWN.
- * tile_tokens: tokens per tile, a multiple of 16 in [16, 256]; experts with
- * more rows take several tiles.  a_s and b_s must be 16-byte aligned. */
-int epsb_grouped_gemm_fp8_tn(int mode, const void* A, const float* a_s, const void* B, const float* b_s,
-                             const int32_t* excl, int num_experts, int64_t max_rows, int64_t N, int64_t K, void* C,
-                             const float* row_w, int32_t* status, int tile_tokens, int sm_count, void* stream);
-
 /* bf16 x bf16 -> bf16 grouped GEMM (tcgen05 kind::f16, accumulators resident in TMEM over the whole K extent):
  * for local expert e, C[m,:] = A[m,:] * B[e]^T over rows [excl[e], excl[e+1]), fp32 accumulation, one rounding.
  * ref: AokGroupedGemm::run (src/executor/aok_grouped_gemm.cu:22-37), the op executor.aok_run

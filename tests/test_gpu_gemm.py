@@ -110,78 +110,6 @@ def test_gemm_down_weighted(cuda, oracle, rows, N, K):
     assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
 
 
-TN_CASES = [
-    # rows per expert, N, K, tile_tokens
-    ([128], 256, 128, 128),
-    ([1], 128, 256, 16),
-    ([130, 0, 7], 256, 512, 144),
-    ([130, 0, 7], 256, 512, 64),
-    ([64] * 16, 2048, 1408 - 1408 % 128, 80),
-    ([17, 33, 0, 160, 161, 1, 77, 256], 512, 2048, 160),
-    ([300, 5, 0, 129, 128, 1, 77, 256], 384, 1024, 256),
-    ([40, 9, 100], 256, 1408, 48),          # K/128 = 11: scalar scale loads, odd batch tail
-]
-
-
-@pytest.mark.parametrize("rows,N,K,tile", TN_CASES)
-def test_gemm_token_n_plain(cuda, oracle, rows, N, K, tile):
-    from eps_b200 import ops
-
-    rng = np.random.default_rng(N + K + len(rows) + tile)
-    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, rows, N, K)
-    status = torch.zeros(4, dtype=torch.int32, device=cuda)
-    C = torch.full((max_rows, N), 7.0, dtype=torch.bfloat16, device=cuda)
-    ops.grouped_gemm_fp8(ops.GEMM_PLAIN, _dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda),
-                         _dev(excl, cuda), out=C, status=status, tile_tokens=tile)
-    torch.cuda.synchronize()
-    _check_status(status)
-    want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl)
-    got = C.float().cpu().numpy()
-    rms = np.sqrt(np.mean(want[:D] ** 2)) if D else 1.0
-    # fp32 summation-order differences (vs RMS) plus the bf16 rounding of the output itself (2^-8 relative)
-    assert np.all(np.abs(got[:D] - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
-    assert np.max(np.abs(got[:D] - want[:D]) / (np.abs(want[:D]) + rms)) <= 2 ** -7
-    assert np.all(got[D:] == 7.0), "rows outside every expert must not be written"
-
-
-@pytest.mark.parametrize("rows,N,K,tile", [([128], 256, 128, 128), ([9, 250, 0, 40], 512, 1408 - 1408 % 128, 96)])
-def test_gemm_token_n_down_matches_tile_kernel(cuda, oracle, rows, N, K, tile):
-    """Token-N and the 128x256 kernel compute the same sums in the same order per K block: their bf16
-    outputs agree to one rounding, and both agree with the oracle."""
-    from eps_b200 import ops
-
-    rng = np.random.default_rng(N * 3 + K)
-    excl, D, max_rows, A, a_s, B, b_s = _make(oracle, rng, rows, N, K)
-    row_w = rng.random(max_rows).astype(np.float32)
-    status = torch.zeros(4, dtype=torch.int32, device=cuda)
-    args = (_dev(A, cuda), _dev(a_s, cuda), _dev(B, cuda), _dev(b_s, cuda), _dev(excl, cuda))
-    C1 = ops.grouped_gemm_fp8(ops.GEMM_DOWN, *args, row_w=_dev(row_w, cuda), status=status)
-    C2 = ops.grouped_gemm_fp8(ops.GEMM_DOWN, *args, row_w=_dev(row_w, cuda), status=status, tile_tokens=tile)
-    torch.cuda.synchronize()
-    _check_status(status)
-    want = oracle.grouped_gemm_fp8(A, a_s, B, b_s, excl) * row_w[:, None]
-    g1, g2 = C1.float().cpu().numpy()[:D], C2.float().cpu().numpy()[:D]
-    rms = np.sqrt(np.mean(want[:D] ** 2))
-    assert np.all(np.abs(g2 - want[:D]) <= 2e-2 * rms + 2.0 ** -8 * np.abs(want[:D]))
-    assert np.max(np.abs(g2 - g1)) <= 2 ** -7 * (np.max(np.abs(want[:D])) + rms)
-
-
-def test_gemm_token_n_errors(cuda):
-    from eps_b200 import ops
-    from eps_b200._lib import EpsError
-
-    A = torch.zeros((16, 128), dtype=torch.uint8, device=cuda)
-    a_s = torch.zeros((16, 1), device=cuda)
-    B = torch.zeros((1, 128, 128), dtype=torch.uint8, device=cuda)
-    b_s = torch.zeros((1, 1, 1), device=cuda)
-    excl = torch.tensor([0, 16], dtype=torch.int32, device=cuda)
-    for tile in (8, 24, 272):
-        with pytest.raises(EpsError):
-            ops.grouped_gemm_fp8(ops.GEMM_PLAIN, A, a_s, B, b_s, excl, tile_tokens=tile)
-    with pytest.raises(EpsError):
-        ops.grouped_gemm_fp8(ops.GEMM_GATEUP, A, a_s, B.expand(1, 128, 128).reshape(1, 128, 128), b_s, excl, tile_tokens=16)
-
-
 def test_gemm_sm_count_limit(cuda, oracle):
     """The sm_count argument (the sm_count of the reference's aok_create) changes the grid, not the result."""
     from eps_b200 import ops
