@@ -46,7 +46,7 @@ SIGNATURES = {
     "epsb_router_topk": [_I, _P, _I, _P, _I, _I, _I, _I, _I, c_float, _I, _P, _P, _P],
     "epsb_grouped_gemm_fp8_gather": [_I, _P, _P, _L, _P, _P, _P, _P, _I, _L, _L, _L, _P, _P, _P, _P, _I, _P],
     "epsb_gemm_row_sources": [_P, _P, _I, _I, _P, _I, _P, _L, _P, _P, _P],
-    "epsb_grouped_gemm_bf16": [_P, _P, _P, _I, _L, _L, _L, _P, _P, _I, _P],
+    "epsb_grouped_gemm_bf16": [_P, _P, _P, _I, _L, _L, _L, _L, _P, _P, _I, _P],
     "epsb_gather_row_weights": [_P, _P, _P, _I, _L, _P, _P],
     "epsb_oep_arrange_plan": [_P, _L, _L, _I, _P, _P, _P, _P],
     "epsb_exchange_put_ids": [_P, _I, _P, _P, _P, _L, _P],

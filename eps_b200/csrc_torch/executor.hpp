@@ -91,8 +91,9 @@ class AokGroupedGemm : public GroupedGemmBase {
   void run(RunParams p, cudaStream_t stream) override {
     if (p.biases != nullptr) throw std::runtime_error("biases are not supported");
     const char* B = static_cast<const char*>(p.B) + (int64_t)p.expert_begin * p.gemm_n * p.gemm_k * 2;
-    executor_raise_if(epsb_grouped_gemm_bf16(p.A, B, window(p), p.num_experts_per_stage, p.max_num_tokens, p.gemm_n,
-                                             p.gemm_k, p.C, status_, sm_count_, stream));
+    executor_raise_if(epsb_grouped_gemm_bf16(p.A, B, window(p), p.num_experts_per_stage, p.max_num_tokens,
+                                             p.total_rows > 0 ? p.total_rows : 0, p.gemm_n, p.gemm_k, p.C, status_,
+                                             sm_count_, stream));
   }
 };
 

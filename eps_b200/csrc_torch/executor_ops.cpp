@@ -57,7 +57,7 @@ void check_fp8_scales(const at::Tensor& A, const at::Tensor& A_scale, const at::
 }
 
 void aok_run(fptr_t ptr, const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const at::Tensor& exclusive_sum,
-             int64_t /*num_tokens_hint*/, int64_t max_num_tokens, at::Tensor& /*ws*/) {
+             int64_t num_tokens_hint, int64_t max_num_tokens, at::Tensor& /*ws*/) {
   auto* h = handle(ptr);
   check_gemm_shapes(h, A, B, C, exclusive_sum, max_num_tokens, B.size(1));
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 && C.scalar_type() == at::kBFloat16,
@@ -71,6 +71,7 @@ void aok_run(fptr_t ptr, const at::Tensor& A, const at::Tensor& B, at::Tensor& C
   p.gemm_k = B.size(2);
   p.num_experts_per_stage = (int)B.size(0);
   p.max_num_tokens = max_num_tokens;
+  p.total_rows = num_tokens_hint;
   h->bf16.run(p, current_stream());
 }
 

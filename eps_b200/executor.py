@@ -32,7 +32,7 @@ class AokGroupedGemm:
         if self.status is None or self.status.device != A.device:
             self.status = torch.zeros(4, dtype=torch.int32, device=A.device)
         if B_scale is None:
-            return ops.grouped_gemm_bf16(A, B, exclusive_sum, status=self.status)
+            return ops.grouped_gemm_bf16(A, B, exclusive_sum, status=self.status, rows_hint=int(num_tokens_hint or 0))
         if A_scale is None:
             raise EpsError("the FP8 grouped GEMM needs A_scale next to B_scale")
         return ops.grouped_gemm_fp8(ops.GEMM_PLAIN, A, A_scale, B, B_scale, exclusive_sum, status=self.status)

@@ -1,7 +1,7 @@
 """Timing of the FP8 grouped GEMM alone, at benchmark shapes.
 
   python -m eps_b200.gemm_bench [--mode down|plain|gateup|bf16] [--experts 256] [--rows 128] [--jitter 0]
-                                [--N 7168] [--K 2048] [--iters 10]
+                                [--N 7168] [--K 2048] [--iters 10] [--single]
 
 --rows is the mean row count per expert, --jitter the standard deviation of a seeded normal spread around it
 (the routed layer at 4096 tokens, top-8, 256 experts has 128 +- 11).  --mode bf16 times the bf16 x bf16 grouped
@@ -36,7 +36,7 @@ def make_problem(experts, rows, jitter, N, K, dev, seed=1):
     return D, excl, A, a_s, B, b_s
 
 
-def run(mode, experts, rows, jitter, N, K, iters):
+def run(mode, experts, rows, jitter, N, K, iters, single=False):
     dev = torch.device("cuda")
     D, excl, A, a_s, B, b_s = make_problem(experts, rows, jitter, N, K, dev)
     if mode == -1:
@@ -53,7 +53,7 @@ def run(mode, experts, rows, jitter, N, K, iters):
 
     def launch():
         if mode == -1:
-            ops.grouped_gemm_bf16(A, B, excl, out=out, status=status)
+            ops.grouped_gemm_bf16(A, B, excl, out=out, status=status, rows_hint=1 if single else D)
         else:
             ops.grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=out, out_scales=outs, row_w=row_w, status=status)
 
@@ -85,8 +85,9 @@ def main():
     ap.add_argument("--N", type=int, default=7168)
     ap.add_argument("--K", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--single", action="store_true", help="bf16: 128-row tiles on single CTAs even for large experts")
     a = ap.parse_args()
-    print(json.dumps(run(MODES[a.mode], a.experts, a.rows, a.jitter, a.N, a.K, a.iters)))
+    print(json.dumps(run(MODES[a.mode], a.experts, a.rows, a.jitter, a.N, a.K, a.iters, a.single)))
 
 
 if __name__ == "__main__":

@@ -348,9 +348,10 @@ def grouped_gemm_fp8(mode, A, a_s, B, b_s, excl, out=None, out_scales=None, row_
     return (C, c_s) if mode == GEMM_GATEUP else C
 
 
-def grouped_gemm_bf16(A, B, excl, out=None, status=None, sm_count=0):
+def grouped_gemm_bf16(A, B, excl, out=None, status=None, sm_count=0, rows_hint=0):
     """bf16 x bf16 -> bf16 grouped GEMM (the reference's aok_run): A [max_rows, K], B [E, N, K], excl [E+1] int32;
-    rows [excl[e], excl[e+1]) of A times B[e]^T, fp32 accumulation."""
+    rows [excl[e], excl[e+1]) of A times B[e]^T, fp32 accumulation.  rows_hint = expected number of rows (the
+    reference's num_tokens_hint; 0 = unknown): picks 256-row tiles on CTA pairs for large experts."""
     _check(A, "A", torch.bfloat16, 2)
     _check(B, "B", torch.bfloat16, 3)
     _check(excl, "exclusive_sum", torch.int32, 1)
@@ -361,6 +362,6 @@ def grouped_gemm_bf16(A, B, excl, out=None, status=None, sm_count=0):
     if excl.numel() != E + 1:
         raise EpsError(f"exclusive_sum must have {E + 1} entries")
     C = out if out is not None else torch.empty((max_rows, N), dtype=torch.bfloat16, device=A.device)
-    call("epsb_grouped_gemm_bf16", ptr(A), ptr(B), ptr(excl), E, max_rows, N, K, ptr(C), ptr(status), int(sm_count),
-         stream_ptr())
+    call("epsb_grouped_gemm_bf16", ptr(A), ptr(B), ptr(excl), E, max_rows, int(rows_hint), N, K, ptr(C), ptr(status),
+         int(sm_count), stream_ptr())
     return C

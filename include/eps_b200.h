@@ -349,9 +349,13 @@ int epsb_gemm_row_sources(const int32_t* gemm_map, const int32_t* excl, int num_
  *      (src/executor/bindings/aok_grouped_gemm_ops.cu:39-84), SM90_GROUPED_GEMM::Launch
  *      (src/gemm/aok_grouped_gemm/src/operations/hopper_grouped_gemm_kernel.h:322-400; alpha 1, beta 0).
  * A [max_rows, K] bf16 row-major, B [EL, N, K] bf16 (K contiguous), C [max_rows, N] bf16.  K % 64 == 0, N % 128 == 0.
- * excl, status, sm_count as in epsb_grouped_gemm_fp8.  No workspace (aok_get_workspace_size is 0). */
+ * excl, status, sm_count as in epsb_grouped_gemm_fp8.  No workspace (aok_get_workspace_size is 0).
+ * rows_hint: the number of rows the caller expects (the reference's num_tokens_hint; 0 = unknown, max_rows is used).
+ * It only picks the tile form: with at least 512 expected rows per expert and N % 256 == 0, pairs of CTAs compute
+ * 256 x 256 tiles (tcgen05.mma.cta_group::2, each CTA stages half of the weight rows), else single CTAs 128 x 256. */
 int epsb_grouped_gemm_bf16(const void* A, const void* B, const int32_t* excl, int num_experts, int64_t max_rows,
-                           int64_t N, int64_t K, void* C, int32_t* status, int sm_count, void* stream);
+                           int64_t rows_hint, int64_t N, int64_t K, void* C, int32_t* status, int sm_count,
+                           void* stream);
 
 /* Gathers the per-GEMM-row gate weight: row_w[d] = w_recv[gemm_map[d]] for
  * d < excl[EL] (w_recv is [R,k] flat, gemm_map holds row*k+slot). */

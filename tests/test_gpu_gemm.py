@@ -138,21 +138,26 @@ def test_gemm_errors(cuda):
                              torch.zeros((1, 1, 1), device=cuda), torch.zeros(2, dtype=torch.int32, device=cuda))
 
 
+@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("rows,N,K", [([200, 17, 0, 129], 512, 256), ([1, 128, 300], 384, 192), ([64] * 8, 1024, 2048),
-                                      ([700], 256, 64)])
-def test_grouped_gemm_bf16_vs_fp32_reference(cuda, rows, N, K):
+                                      ([700], 256, 64), ([300, 257, 256, 1, 0, 511], 512, 256),
+                                      ([1024, 1000, 1030], 256, 128)])
+def test_grouped_gemm_bf16_vs_fp32_reference(cuda, rows, N, K, pairs):
     """The bf16 grouped GEMM (the reference's aok_run) against a plain fp32 matmul of the same bf16 operands: fp32
-    accumulation and one rounding on both sides, so the results agree to one bf16 ulp (summation order differs)."""
+    accumulation and one rounding on both sides, so the results agree to one bf16 ulp (summation order differs).
+    pairs: the row hint promises experts large enough for 256-row tiles on CTA pairs (cta_group::2); N % 256 != 0
+    keeps single CTAs either way."""
     from eps_b200 import ops
 
     g = torch.Generator().manual_seed(len(rows) * 1000 + N)
     E, D = len(rows), sum(rows)
+    max_rows = max(D + 5, E * 512) if pairs else D + 5
     excl = torch.tensor([0] + list(np.cumsum(rows)), dtype=torch.int32, device=cuda)
-    A = torch.randn((D + 5, K), generator=g).to(torch.bfloat16).to(cuda)
+    A = torch.randn((max_rows, K), generator=g).to(torch.bfloat16).to(cuda)
     B = (torch.randn((E, N, K), generator=g) * 0.05).to(torch.bfloat16).to(cuda)
     status = torch.zeros(4, dtype=torch.int32, device=cuda)
-    out = torch.full((D + 5, N), 7.0, dtype=torch.bfloat16, device=cuda)
-    ops.grouped_gemm_bf16(A, B, excl, out=out, status=status)
+    out = torch.full((max_rows, N), 7.0, dtype=torch.bfloat16, device=cuda)
+    ops.grouped_gemm_bf16(A, B, excl, out=out, status=status, rows_hint=max_rows if pairs else 1)
     torch.cuda.synchronize()
     _check_status(status)
     ex = excl.cpu().numpy()
