@@ -29,6 +29,10 @@ class CommunicatorParams:
     num_ranks_per_node: int
 
 
+class SymmetricMemoryUnavailable(RuntimeError):
+    """Raised by Communicator.symm_alloc on EVERY rank when any rank could not allocate or map the shared regions."""
+
+
 class Communicator:
     """One expert-parallel group.  `group` is a torch.distributed process group (None = default group)."""
 
@@ -51,6 +55,7 @@ class Communicator:
                 raise RuntimeError("multi-node expert parallelism is not supported: one NVSwitch box only")
         if transport not in ("auto", "ipc", "nccl"):
             raise RuntimeError(f"transport must be 'auto', 'ipc' or 'nccl', got {transport!r}")
+        self.transport_is_a_choice = transport == "auto"   # "auto" may fall back from "ipc" to "nccl" (all ranks together)
         if transport == "auto":
             on_gpu = self.world > 1 and dist.get_backend(group) == "nccl"
             transport = "ipc" if on_gpu and self.world <= 8 else "nccl"
@@ -80,25 +85,52 @@ class Communicator:
 
     def symm_alloc(self, nbytes: int):
         """Collective.  Allocates `nbytes` of zeroed device memory on every rank and maps every rank's block into
-        every process: -> (this rank's pointer, [pointer of rank r's block in this process for r in range(world)])."""
+        every process: -> (this rank's pointer, [pointer of rank r's block in this process for r in range(world)]).
+        If any rank cannot allocate or map (no peer access, no IPC between the processes), every rank releases what
+        it holds and raises SymmetricMemoryUnavailable, so that all ranks take the same decision."""
         local = ctypes.c_void_p()
         handle = (ctypes.c_uint8 * 64)()
-        _lib.call("epsb_symm_alloc", int(nbytes), ctypes.byref(local), handle)
+        err = None
+        try:
+            _lib.call("epsb_symm_alloc", int(nbytes), ctypes.byref(local), handle)
+        except _lib.EpsError as e:
+            err = e
+            local = ctypes.c_void_p(0)
         peers = [local.value] * self.world
         if self.world > 1:
             dev = torch.device("cuda", torch.cuda.current_device())
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
             allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=dev)
             dist.all_gather_into_tensor(allh.view(-1), mine, group=self.group)
-            allh = allh.cpu()
-            for r in range(self.world):
-                if r == self.rank:
-                    continue
-                h = (ctypes.c_uint8 * 64)(*allh[r].tolist())
-                p = ctypes.c_void_p()
-                _lib.call("epsb_symm_open", h, ctypes.byref(p))
-                peers[r] = p.value
-            dist.barrier(group=self.group)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            opened = []
+            if int(ok.item()) == 1:
+                allh = allh.cpu()
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    h = (ctypes.c_uint8 * 64)(*allh[r].tolist())
+                    p = ctypes.c_void_p()
+                    try:
+                        _lib.call("epsb_symm_open", h, ctypes.byref(p))
+                    except _lib.EpsError as e:
+                        err = e
+                        break
+                    peers[r] = p.value
+                    opened.append(p.value)
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)   # doubles as the barrier after the opens
+            if int(ok.item()) == 0:
+                for p in opened:
+                    _lib.call("epsb_symm_close", p)
+                dist.barrier(group=self.group)
+                if local.value:
+                    _lib.call("epsb_symm_free", local.value)
+                raise SymmetricMemoryUnavailable(
+                    f"symmetric memory over CUDA IPC is not available on every rank ({err or 'a peer failed'})")
+        elif err is not None:
+            raise err
         self._regions.append((local.value, peers))
         return local.value, peers
 

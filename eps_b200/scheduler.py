@@ -11,13 +11,14 @@ path uses the slots the reference already has: `input_quanted`, `input_scales`, 
 from __future__ import annotations
 
 import ctypes
+import sys
 
 import numpy as np
 import torch
 
 from . import _lib, ops
 from ._lib import EpsError
-from .communication import Communicator
+from .communication import Communicator, SymmetricMemoryUnavailable
 
 ARENA_IDX, ARENA_WEIGHTS, ARENA_HIDDEN, ARENA_SCALES, ARENA_OUT, ARENA_RECV_PLAN = range(6)
 PUT_META, PUT_SCALES, PUT_HIDDEN = 1, 2, 4
@@ -200,8 +201,16 @@ class Scheduler:
         self.hidden_dtype = in_dt
         if self.W > 1 and self.comm.transport == "ipc":
             # device-side exchange: the receive arenas live in the symmetric region, nothing is staged for sending
-            self.peer = PeerExchange(self.comm, self.max_tok, self.local_num_experts, top_k, hidden_size,
-                                     torch.empty((), dtype=in_dt).element_size(), input_scales_dim, dev)
+            try:
+                self.peer = PeerExchange(self.comm, self.max_tok, self.local_num_experts, top_k, hidden_size,
+                                         torch.empty((), dtype=in_dt).element_size(), input_scales_dim, dev)
+            except SymmetricMemoryUnavailable as e:
+                # raised on every rank together; a transport the caller did not insist on gives way to the other one
+                if not self.comm.transport_is_a_choice:
+                    raise
+                print(f"eps_b200: {e}; expert-parallel exchange falls back to the NCCL transport", file=sys.stderr)
+                self.comm.transport = "nccl"
+        if self.peer is not None:
             self.recv_out = self.peer.recv_out
             self._select_arenas()
         else:
