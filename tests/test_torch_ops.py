@@ -127,6 +127,74 @@ def test_executor_ops(cuda, oracle, eps_pkg):
 
 
 @pytest.mark.gpu
+def test_ffn_executors_behind_the_contract_types(cuda, oracle, eps_pkg):
+    """GemmExecutor / SharedExperts / dense / batched GEMM / dense SwiGLU (the reference's contract types
+    GemmExecutorInterface, SharedExpertsInterface, DenseGemmInterface, BatchedGemmInterface, DenseActivationInterface)
+    give bit for bit what the same kernels give when called one by one, and the FFN agrees with the oracle."""
+    from eps.executor import GemmExecutor, SharedExperts, batched_gemm_fp8, dense_gemm_fp8, dense_silu
+
+    from eps_b200 import ops
+
+    rng = np.random.default_rng(11)
+    E, H, I = 4, 512, 256
+    rows = [130, 0, 64, 7]
+    D = sum(rows)
+    excl = torch.tensor([0] + list(np.cumsum(rows)), dtype=torch.int32, device=cuda)
+    dv = lambda t: torch.from_numpy(np.ascontiguousarray(t)).to(cuda)
+    a = oracle.bf16_bits(rng.standard_normal((D, H)).astype(np.float32))
+    Aq, a_s = oracle.quant_1x128(a)
+    wgu, wgu_s = oracle.quant_block128((rng.standard_normal((E, 2 * I, H)) * 0.03).astype(np.float32))
+    wd, wd_s = oracle.quant_block128((rng.standard_normal((E, H, I)) * 0.03).astype(np.float32))
+    row_w = rng.random(D).astype(np.float32)
+    A, As = dv(Aq), dv(a_s)
+    # the kernels one by one
+    act, act_s = ops.grouped_gemm_fp8(ops.GEMM_GATEUP, A, As, dv(wgu), dv(wgu_s), excl)
+    want = ops.grouped_gemm_fp8(ops.GEMM_DOWN, act, act_s, dv(wd), dv(wd_s), excl, row_w=dv(row_w))
+    ex = GemmExecutor(dv(wgu), dv(wgu_s), dv(wd), dv(wd_s))
+    got = ex.run(A, As, excl, row_weights=dv(row_w))
+    torch.cuda.synchronize()
+    assert ex.status().tolist()[0] == 0
+    assert torch.equal(got[:D], want[:D])
+    # two stages: each stage writes its own experts' rows
+    out2 = torch.zeros_like(got)
+    for s in range(2):
+        ex.run(A, As, excl, num_stages=2, stage_idx=s, row_weights=dv(row_w), out=out2)
+    assert torch.equal(out2[:D], want[:D])
+    with pytest.raises(RuntimeError, match="Invalid num_stages"):
+        ex.run(A, As, excl, num_stages=3)
+    ex.destroy()
+    # against the oracle: the down GEMM of the requantised activation, x the row's weight (the gate/up half has its
+    # own oracle test in test_gpu_gemm.py)
+    y = oracle.grouped_gemm_fp8(act.cpu().numpy(), act_s.cpu().numpy(), wd, wd_s, excl.cpu().numpy()) * row_w[:, None]
+    rms = float(np.sqrt(np.mean(y ** 2)))
+    assert np.all(np.abs(got[:D].float().cpu().numpy() - y) <= 2e-2 * rms + 2.0 ** -8 * np.abs(y))
+    # shared expert = one expert over all rows
+    sh = SharedExperts(dv(wgu[:1]), dv(wgu_s[:1]), dv(wd[:1]), dv(wd_s[:1]))
+    e1 = torch.tensor([0, D], dtype=torch.int32, device=cuda)
+    a1, a1s = ops.grouped_gemm_fp8(ops.GEMM_GATEUP, A, As, dv(wgu[:1]), dv(wgu_s[:1]), e1)
+    w1 = ops.grouped_gemm_fp8(ops.GEMM_DOWN, a1, a1s, dv(wd[:1]), dv(wd_s[:1]), e1)
+    assert torch.equal(sh.run(A, As), w1)
+    sh.destroy()
+    # dense and batched GEMM = the grouped kernel on one / G equal row ranges
+    Bq, Bs = dv(wd[0]), dv(wd_s[0])          # [H, I] as a dense [N, K] weight
+    X, Xs = act[:D].contiguous(), act_s[:D].contiguous()
+    dense = dense_gemm_fp8(X, Xs, Bq, Bs)
+    ref = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, X, Xs, dv(wd[:1]), dv(wd_s[:1]), e1)
+    assert torch.equal(dense, ref)
+    G, M = 3, 40
+    Xb, Xbs = X[:G * M].reshape(G, M, I).contiguous(), Xs[:G * M].reshape(G, M, I // 128).contiguous()
+    bat = batched_gemm_fp8(Xb, Xbs, dv(wd[:G]), dv(wd_s[:G]))
+    eb = torch.tensor([0, M, 2 * M, 3 * M], dtype=torch.int32, device=cuda)
+    refb = ops.grouped_gemm_fp8(ops.GEMM_PLAIN, X[:G * M].contiguous(), Xs[:G * M].contiguous(), dv(wd[:G]),
+                                dv(wd_s[:G]), eb)
+    assert torch.equal(bat.reshape(G * M, H), refb)
+    gu_bf = torch.randn((33, 512), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(cuda)
+    r = torch.zeros((33, 256), dtype=torch.bfloat16, device=cuda)
+    ops.silu_run(gu_bf, r, torch.tensor([0, 33], dtype=torch.int32, device=cuda), 1)
+    assert torch.equal(dense_silu(gu_bf), r)
+
+
+@pytest.mark.gpu
 def test_utils_ops(cuda, eps_pkg):
     from eps.utils import ops as uops
 
