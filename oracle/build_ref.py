@@ -1,7 +1,7 @@
 """Compiles the reference's own arch-agnostic kernels (in place, from the reference checkout) plus
 oracle/ref_harness.cu into oracle/_ref/libeps_ref.so for sm_100a.
 
-TEST INFRASTRUCTURE ONLY.  Needs the reference checkout (default /root/reference, or $EPS_REFERENCE);
+TEST INFRASTRUCTURE ONLY.  Needs the reference checkout ($EPS_REFERENCE, or the default location in the code);
 where it is absent the prebuilt library, if any, is used as is.  Nothing from the reference is copied.
 """
 from __future__ import annotations
