@@ -235,6 +235,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (diagnostics only)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (diagnostics only)")
     ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1)")
+    ap.add_argument("--shared-late", action="store_true",
+                    help="diagnostics: run the shared expert after the routed experts instead of under the dispatch")
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="repeat the timed block of --steps steps until this much time has been timed")
     ap.add_argument("--parity-tokens", type=int, default=64, help="output rows per rank checked against the oracle")
@@ -280,6 +282,7 @@ def main():
     from eps_b200.layer import build_synthetic_layer, synthetic_expert_codes
 
     layer = build_synthetic_layer(cfg, comm, dev, stages)
+    layer.shared_under_dispatch = not args.shared_late
     T, H, k = cfg.tokens_per_rank, cfg.hidden, cfg.top_k
     x_h = workloads.make_tokens(cfg, rank).pin_memory()
     idx_h, w_h = workloads.make_routing(cfg, rank)
@@ -465,7 +468,8 @@ def main():
             roofline["bus_gbs"] = {"dispatch": float(t[0].item()), "combine": float(t[1].item()), "peak": 900.0,
                                    "rank0": bus, "note": "min over ranks of max(bytes out, bytes in) / CUDA-event time of the exchange on its stream"
                                            "; with the device-side transport the dispatch time covers plan exchange + "
-                                           "permute-on-send + flag wait, the combine time the fused local reduce + store",
+                                           "permute-on-send (+ the flag wait when there is no shared expert to run "
+                                           "under it), the combine time the fused local reduce + store",
                                    "transport": comm.transport}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -73,6 +73,8 @@ class MoELayerFP8:
             self._sh_excl = {}
         self.kernel_launches = 0
         self.shared_sm_reserve = 4   # SMs the shared expert's GEMMs leave to the plan and gather kernels (EP=1)
+        # device-side exchange: run the shared expert between this rank's put and the wait for the peers' rows
+        self.shared_under_dispatch = True
         self.gateup_events = None  # optional (start, end) torch.cuda.Event pair recorded around the gate/up GEMM
         # optional list; with ep_world_size > 1 every exchange appends (kind, start event, end event, stage) so that a
         # caller can report bus bandwidth (bytes per exchange: Scheduler.exchange_bytes, after the timed region)
@@ -105,10 +107,21 @@ class MoELayerFP8:
         # device-side exchange with one stage: the FP8 rows and their scales travel with the expert ids
         eager = sched.peer is not None and S == 1
         mark = self._exchange_mark("dispatch", 0, torch.cuda.current_stream()) if eager else None
-        excl, n_recv = sched.rendezvous_and_plan(expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1,
-                                                 max_cluster=1 if shared_done is not None else 0,
-                                                 payload=(xq, xs) if eager else None)
-        self._exchange_done(mark, torch.cuda.current_stream())
+        early = []   # device-side exchange: the shared expert runs while the peers' rows are on their way
+        marks = [mark]
+
+        def shared_under_dispatch():
+            # the exchange's own time ends with this rank's put; what follows is compute, then the flag wait
+            self._exchange_done(marks[0], torch.cuda.current_stream())
+            marks[0] = None
+            early.append(self._shared_expert(xq, xs, T))
+
+        excl, n_recv = sched.rendezvous_and_plan(
+            expert_indices, expert_weights, Tg, S, True, host_sync=self.W > 1,
+            max_cluster=1 if shared_done is not None else 0, payload=(xq, xs) if eager else None,
+            after_put=shared_under_dispatch if (self.shared_under_dispatch and sched.peer is not None
+                                                and self.shared is not None and T > 0) else None)
+        self._exchange_done(marks[0], torch.cuda.current_stream())
         # source plans, expert plans + (NCCL transport: index gather, receive plan | device-side exchange: publish,
         # receive plans, put, wait) or the index gather of a world of one
         n += 2 + (4 if sched.peer is not None else (2 if self.W > 1 else 1))
@@ -198,7 +211,8 @@ class MoELayerFP8:
                 n += 4 if (self.gemm_gathers_rows or not self.direct_sources) else 6
             all_back = torch.cuda.Event()
             all_back.record(comm_stream)
-        shared_out = self._shared_expert(xq, xs, T) if self.W > 1 else shared_out
+        if self.W > 1:
+            shared_out = early[0] if early else self._shared_expert(xq, xs, T)
         if out is None:
             out = torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device)
         if self.W > 1:

@@ -248,7 +248,7 @@ class Scheduler:
 
     def rendezvous_and_plan(self, expert_indices: torch.Tensor, expert_scales: torch.Tensor, num_global_tokens,
                             num_stages, input_quanted, host_sync: bool = True, max_cluster: int = 0,
-                            payload=None):
+                            payload=None, after_put=None):
         """-> (exclusive_sum [EL+1] int32 on the device, number of unique rows this rank receives).
 
         With a world of one and host_sync=False nothing is copied to the host and the second value is the
@@ -256,7 +256,8 @@ class Scheduler:
         max_cluster caps the CTAs of the plan kernels (0 = up to 8).
         With the device-side exchange nothing is read on the host either: the second value is the arena size, and
         `payload` = (hidden_states, input_scales) lets the rows travel in the same launch as the expert ids
-        (`dispatch` is then a no-op)."""
+        (`dispatch` is then a no-op); `after_put` is called between this rank's put and the wait for the peers'
+        rows, so that work which needs no peer (the shared expert) runs while those rows are on their way."""
         T = expert_indices.shape[0]
         ctx = self.context = self.get_context(T, num_global_tokens, num_stages, input_quanted)
         W, S, k = self.W, num_stages, self.top_k
@@ -290,6 +291,8 @@ class Scheduler:
                     raise EpsError(f"hidden_states must have dtype {self.hidden_dtype}, got {hidden.dtype}")
                 mask |= PUT_HIDDEN | (PUT_SCALES if scales is not None else 0)
             pe.put(FLAG_META, -1, mask, expert_indices, expert_scales, hidden, scales, ctx.send_map, ctx.send_incl, T, S)
+            if after_put is not None:
+                after_put()
             pe.wait(FLAG_META)
             ctx.n_recv = None
             rows_bound = self.arena_rows
