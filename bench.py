@@ -235,6 +235,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (diagnostics only)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (diagnostics only)")
     ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1)")
+    ap.add_argument("--graph", action="store_true",
+                    help="diagnostics (N=1): also time the resident step replayed as one CUDA graph (key cuda_graph)")
     ap.add_argument("--shared-late", action="store_true",
                     help="diagnostics: run the shared expert after the routed experts instead of under the dispatch")
     ap.add_argument("--min-seconds", type=float, default=2.0,
@@ -362,6 +364,13 @@ def main():
     layer.exchange_events_done = layer.exchange_events
     layer.exchange_events = None
     blocks_e2e = timed_blocks(step_e2e, host_path=True)
+    graph_info = None
+    if args.graph and world == 1:
+        # the same resident step replayed as one CUDA graph (diagnostics: what the host's launch work costs)
+        captured = layer.capture(x_d, idx_d, w_d, out_d, Tg)
+        blocks_g = timed_blocks(captured.replay)
+        graph_info = {"ms_per_step": statistics.median(blocks_g) / args.steps, "timed_blocks": len(blocks_g),
+                      "kernels_in_graph": captured.kernel_launches}
     clocks = sampler.stop() if rank == 0 else None
     layer.check_status()
 
@@ -499,6 +508,8 @@ def main():
             "gpu_launches": layer.kernel_launches * args.steps,
             "roofline": roofline, "parity": parity, "cpu_baseline": cpu, "clocks": clocks,
         }
+        if graph_info is not None:
+            line["cuda_graph"] = graph_info
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -226,6 +226,14 @@ class MoELayerFP8:
         self.kernel_launches = n
         return out
 
+    def capture(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor, out: torch.Tensor,
+                num_global_tokens: int | None = None) -> "CapturedStep":
+        """One layer step as a CUDA graph over these four tensors: `replay()` runs the step on whatever they hold
+        then.  For steps whose time is the host's launch work rather than the GPU's (decode-sized batches: ten
+        launches of a few microseconds of GPU time each).  World of one only: the device-side exchange numbers its
+        calls on the host."""
+        return CapturedStep(self, x, expert_indices, expert_weights, out, num_global_tokens)
+
     def forward_routed(self, x: torch.Tensor, router_logits: torch.Tensor, router_bias: torch.Tensor | None,
                        num_expert_groups: int = 1, topk_groups: int = 1, route_scale: float = 1.0,
                        num_zero_experts: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -328,6 +336,36 @@ class MoELayerFP8:
         st = self.status.cpu().tolist()
         if st[0] != 0:
             raise EpsError(f"grouped GEMM gave up on a bounded wait (code {st[0]}, CTA {st[1]})")
+
+
+class CapturedStep:
+    """A captured MoELayerFP8.forward (see MoELayerFP8.capture).  The graph holds the plan and GEMM buffers of its
+    step; the layer's eager entry points stay usable beside it, but not while a replay is in flight."""
+
+    def __init__(self, layer: MoELayerFP8, x, expert_indices, expert_weights, out, num_global_tokens=None):
+        if layer.W != 1:
+            raise EpsError("a layer step can be captured in a world of one only")
+        if out is None or out.shape != (x.shape[0], layer.H) or out.dtype != torch.bfloat16:
+            raise EpsError("capture needs the output tensor [T, H] bfloat16 the replays will write")
+        self.layer, self.out = layer, out
+        self.inputs = (x, expert_indices, expert_weights)
+        ev, gev = layer.exchange_events, layer.gateup_events
+        layer.exchange_events = layer.gateup_events = None   # timing events cannot be recorded inside a graph
+        try:
+            for _ in range(2):   # first-call set-up (function attributes, cached bounds, the side stream) stays outside
+                layer.forward(x, expert_indices, expert_weights, num_global_tokens, out=out)
+            torch.cuda.synchronize()
+            layer.check_status()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                layer.forward(x, expert_indices, expert_weights, num_global_tokens, out=out)
+            self.kernel_launches = layer.kernel_launches
+        finally:
+            layer.exchange_events, layer.gateup_events = ev, gev
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out
 
 
 def synthetic_expert_codes(cfg, expert: int, device, inter: int | None = None):

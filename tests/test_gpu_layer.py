@@ -86,6 +86,39 @@ def test_layer_vs_oracle(cuda, oracle, case):
     assert ok, msg
 
 
+def test_captured_step_replays_equal_eager_calls(cuda, oracle):
+    """A layer step captured as a CUDA graph (two streams: the shared expert beside the plans) gives, on new tokens and
+    new routing written into the captured tensors, bit for bit what the eager call gives."""
+    from eps_b200 import workloads
+    from eps_b200._lib import EpsError
+    from eps_b200.layer import MoELayerFP8
+
+    T, H, I, E, k, nz, sh = 100, 1024, 512, 8, 4, 4, 256
+    cfg = workloads.CONFIGS[0].scaled(tokens_per_rank=T, hidden=H, inter=I, num_experts=E, top_k=k,
+                                      num_zero_experts=nz, shared_inter=sh, bias="normal")
+    dev_w, _ = _weights(cfg, range(E), cuda, oracle)
+    shared, _ = _weights(cfg, [-1], cuda, oracle)
+    layer = MoELayerFP8(H, I, E, k, T, *dev_w, shared=shared)
+    x = workloads.make_tokens(cfg).to(cuda)
+    idx, w = (t.to(cuda) for t in workloads.make_routing(cfg))
+    out = torch.zeros((T, H), dtype=torch.bfloat16, device=cuda)
+    step = layer.capture(x, idx, w, out)
+    for seed in (3, 4):
+        cfg2 = cfg.scaled(cfg_id=seed)
+        x.copy_(workloads.make_tokens(cfg2).to(cuda))
+        idx2, w2 = workloads.make_routing(cfg2)
+        idx.copy_(idx2.to(cuda))
+        w.copy_(w2.to(cuda))
+        got = step.replay().clone()
+        torch.cuda.synchronize()
+        layer.check_status()
+        want = layer.forward(x, idx, w)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    with pytest.raises(EpsError):
+        layer.capture(x, idx, w, None)
+
+
 @pytest.mark.parametrize("cfg_id", [0, 1, 2, 3, 4])
 def test_layer_full_size_sampled(cuda, oracle, cfg_id):
     """Every benchmark configuration at its real hidden / intermediate / expert / top-k / token sizes on one GPU
