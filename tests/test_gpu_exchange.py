@@ -67,7 +67,8 @@ def _free(ranks, regions):
         _lib.call("epsb_symm_free", p)
 
 
-@pytest.mark.parametrize("W,S,E,k,T", [(2, 1, 8, 2, 37), (4, 2, 32, 4, 150), (8, 1, 64, 8, 64), (3, 3, 27, 5, 0)])
+@pytest.mark.parametrize("W,S,E,k,T", [(2, 1, 8, 2, 37), (4, 2, 32, 4, 150), (8, 1, 64, 8, 64), (3, 3, 27, 5, 0),
+                                       (8, 2, 256, 8, 700)])   # the last: plans as multi-CTA clusters, 32 experts per rank
 def test_exchange_lock_step(cuda, oracle, W, S, E, k, T):
     from eps_b200 import _lib, ops
     from eps_b200._lib import call, ptr, stream_ptr
