@@ -43,11 +43,15 @@ class Scheduler {
     int32_t *ret_incl = nullptr, *status = nullptr;
     const int32_t* excl = nullptr;  // the caller's exclusive_sum tensor
     float *zero_scale = nullptr, *row_w = nullptr;
+    int32_t* a_rows = nullptr;   // source row of every GEMM row (direct sources)
     // what prologue recorded
     const void* raw_input = nullptr;
     const void* src_hidden = nullptr;
     const float* src_scales = nullptr;
     float* scales_out = nullptr;
+    const float* src_weights = nullptr;
+    bool direct = false;          // world of one, FP8 path: nothing is staged, GEMM rows are read from the caller's tensors
+    bool sources_ready = false;   // a_rows / row_w of this call have been composed
     bool eager = false;
     bool have_zero = false;   // zero_scale was computed (plan got the gate weights)
     size_t ws_bytes = 0;
@@ -173,10 +177,14 @@ class Scheduler {
                                c.red_map, c.ret_incl, c.status + 2, max_cluster, st));
   }
 
+  // direct (a world of one): in a world of one the receive order IS the send order, so the GEMM rows can be read
+  // straight from the caller's tensors through the composed plans (gemmExpand) and nothing is staged here.
   void prologue(const float* expert_scales, const void* hidden, const float* input_scales, float* recv_input_scales,
-                Context& c, cudaStream_t st, const void* raw_input = nullptr) {
+                Context& c, cudaStream_t st, const void* raw_input = nullptr, bool direct = false) {
     need_ws(c);
     const int T = c.num_tokens, S = c.num_stages, k = p_.topk;
+    c.direct = false;
+    c.sources_ready = false;
     // the identity-expert term reads the raw bf16 tokens: an FP8 caller passes them as raw_input
     c.raw_input = raw_input != nullptr ? raw_input : (p_.fp8_hidden ? nullptr : hidden);
     if (c.input_quanted && (input_scales == nullptr || recv_input_scales == nullptr || p_.input_scales_dim == 0))
@@ -188,6 +196,14 @@ class Scheduler {
       return;
     }
     if (T == 0) return;
+    if (direct) {
+      c.direct = true;
+      c.src_hidden = hidden;
+      c.src_scales = c.input_quanted ? input_scales : nullptr;
+      c.scales_out = c.input_quanted ? recv_input_scales : nullptr;
+      c.src_weights = expert_scales;
+      return;
+    }
     const int64_t bound = send_bound(T);
     raise_if(epsb_gather_rows(expert_scales, wts_.data_ptr(), c.send_map, 1, T, c.send_bounds, 0, S, 0, bound,
                               (int64_t)k * 4, st));
@@ -210,9 +226,26 @@ class Scheduler {
     raise_if(epsb_exchange_wait(x_, slot, c.status, 0, st));
   }
 
+  // a_rows[d] = the token whose row GEMM row d is, row_w[d] = its gate weight for that expert (one kernel per call)
+  void composeSources(Context& c, cudaStream_t st) {
+    if (c.sources_ready) return;
+    raise_if(epsb_gemm_row_sources(c.gemm_map, c.excl, EL_, p_.topk, c.send_map, c.num_tokens, c.src_weights,
+                                   gemm_bound(c), c.a_rows, c.row_w, st));
+    c.sources_ready = true;
+  }
+
   void gemmExpand(void* gemm_input, Context& c, int stage, cudaStream_t st) {
     const int eps = EL_ / c.num_stages;
     const int b0 = stage < 0 ? 0 : eps * stage, b1 = stage < 0 ? EL_ : eps * (stage + 1);
+    if (c.direct) {
+      composeSources(c, st);
+      raise_if(epsb_gather_rows(c.src_hidden, gemm_input, c.a_rows, 1, INT32_MAX, c.excl, b0, b1, 0, gemm_bound(c),
+                                p_.hidden_size * hidden_elem_, st));
+      if (c.scales_out != nullptr)
+        raise_if(epsb_gather_rows(c.src_scales, c.scales_out, c.a_rows, 1, INT32_MAX, c.excl, b0, b1, 0, gemm_bound(c),
+                                  (int64_t)p_.input_scales_dim * 4, st));
+      return;
+    }
     raise_if(epsb_gather_rows(hidden_arena(), gemm_input, c.gemm_map, p_.topk, INT32_MAX, c.excl, b0, b1, 0,
                               gemm_bound(c), p_.hidden_size * hidden_elem_, st));
     if (W_ > 1 && c.scales_out != nullptr)
@@ -231,6 +264,9 @@ class Scheduler {
                                               c.ret_incl, c.num_stages, stage, mr, st));
       return;
     }
+    if (!pre_weighted && c.direct)
+      throw std::runtime_error("the reference-arithmetic local reduce reads the staged gate weights: use eps_prologue, or "
+                               "eps_local_reduce_weighted on rows that carry their weight");
     if (pre_weighted)
       raise_if(epsb_local_reduce(gemm_output, c.red_map, c.ret_incl, p_.topk, W_, c.num_stages, stage, mr,
                                  p_.hidden_size, out_.data_ptr(), st));
@@ -266,6 +302,10 @@ class Scheduler {
 
   // row_w[d] = gate weight of GEMM row d (for the down GEMM's fused weighting); lives in the workspace.
   float* gemmRowWeights(Context& c, cudaStream_t st) {
+    if (c.direct) {
+      composeSources(c, st);
+      return c.row_w;
+    }
     raise_if(epsb_gather_row_weights(wts_arena(), c.gemm_map, c.excl, EL_, gemm_bound(c), c.row_w, st));
     return c.row_w;
   }
@@ -323,6 +363,7 @@ class Scheduler {
     c.red_map = (int32_t*)take(R * k * 4);
     c.ret_incl = (int32_t*)take(n * 4);
     c.row_w = (float*)take(R * std::min<int64_t>(k, EL_) * 4);
+    c.a_rows = (int32_t*)take(R * std::min<int64_t>(k, EL_) * 4);
     c.status = (int32_t*)take(16);
     return off;
   }

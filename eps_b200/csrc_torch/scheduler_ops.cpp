@@ -121,7 +121,8 @@ void prologue_fp8(fptr_t ptr, const at::Tensor& expert_scales, const at::Tensor&
   TORCH_CHECK(is_fp8_codes(hidden_codes), "hidden_states must hold e4m3 codes (uint8 or float8_e4m3fn)");
   TORCH_CHECK(raw_input.scalar_type() == at::kBFloat16, "raw_input must be bfloat16");
   sched(ptr)->prologue(expert_scales.data_ptr<float>(), hidden_codes.data_ptr(), input_scales.data_ptr<float>(),
-                       recv_input_scales.data_ptr<float>(), ctx(context), current_stream(), raw_input.data_ptr());
+                       recv_input_scales.data_ptr<float>(), ctx(context), current_stream(), raw_input.data_ptr(),
+                       /*direct=*/sched(ptr)->worldSize() == 1);
 }
 
 void dispatch(fptr_t ptr, fptr_t context, int64_t stage_idx) {
