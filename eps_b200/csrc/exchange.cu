@@ -295,7 +295,13 @@ put_kernel(Peers peers, PutArgs a) {
   const int n = a.W * a.S;
   const int n_sent = a.T > 0 ? a.send_incl[n - 1] : 0;
   const int hvecs = (int)(a.hidden_row_bytes >> 4);
-  for (int64_t i = warp; i < n_sent; i += n_warps) {
+  // Every rank starts with the rows for its right-hand neighbour and walks the send order cyclically from there: at any
+  // moment the ranks of the box store to DIFFERENT destinations.  (In plain send order all ranks would store to
+  // rank 0 first, then to rank 1, ...: one GPU's ingress at a time carries the whole exchange.)
+  const int first_dest = (a.rank + 1) % a.W;
+  const int64_t shift = first_dest == 0 ? 0 : a.send_incl[first_dest * a.S - 1];
+  for (int64_t i0 = warp; i0 < n_sent; i0 += n_warps) {
+    const int64_t i = i0 + shift < n_sent ? i0 + shift : i0 + shift - n_sent;
     // window j = (dest, stage) of row i: the first j with i < send_incl[j]
     int j = 0;
     for (int j0 = 0; j0 < n; j0 += 32) {
@@ -366,7 +372,10 @@ local_reduce_put_kernel(Peers peers, const uint8_t* __restrict__ y, const int32_
   const int64_t sentinel = (int64_t)ret_incl[W * S - 1] * k;
   const int s0 = stage < 0 ? 0 : stage, s1 = stage < 0 ? S : stage + 1;
   int64_t seen = 0;
-  for (int d = 0; d < W; d++) {
+  // destinations in cyclic order from the right-hand neighbour on: the ranks of the box store to different peers at
+  // any moment instead of all to rank 0, then all to rank 1, ...
+  for (int dd = 0; dd < W; dd++) {
+    const int d = (rank + 1 + dd) % W;
     const int jb = d * S + s0, je = d * S + s1 - 1;
     const int64_t b = jb == 0 ? 0 : ret_incl[jb - 1], e = ret_incl[je];
     uint8_t* dst_base = peers.base[d] + off_out + (int64_t)comb_off[jb] * row_bytes;
@@ -434,7 +443,10 @@ lookup_put_kernel(Peers peers, const int32_t* __restrict__ recv_ids, const int32
   const int64_t n_warps = (int64_t)gridDim.x * kXWarps;
   const int vecs = (int)(row_bytes >> 4);
   const int R = recv_incl[W - 1];
-  for (int64_t q = warp; q < R; q += n_warps) {
+  const int first_dest = (rank + 1) % W;   // cyclic from the right-hand neighbour on, like put_kernel
+  const int64_t shift = first_dest == 0 ? 0 : recv_incl[first_dest - 1];
+  for (int64_t q0 = warp; q0 < R; q0 += n_warps) {
+    const int64_t q = q0 + shift < R ? q0 + shift : q0 + shift - R;
     int r = 0;
     while (r < W - 1 && q >= recv_incl[r]) r++;
     const int64_t begin = r == 0 ? 0 : recv_incl[r - 1];

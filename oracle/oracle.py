@@ -355,31 +355,39 @@ def moe_layer_fp32(x_bits, idx, w, Wgu_q, Wgu_s, Wd_q, Wd_s, requant_act=True, s
     return out
 
 
-def moe_layer_fp32_sampled(x_bits, idx, w, expert_weights, shared=None):
+def moe_layer_fp32_sampled(x_bits, idx, w, expert_weights, shared=None, return_magnitude=False):
     """The standard of moe_layer_fp32 evaluated on a SAMPLE of tokens: rows of x_bits / idx / w are the sampled
     tokens only.  expert_weights(e) -> (Wgu_q [2I,H], Wgu_s [2I/128,H/128], Wd_q [H,I], Wd_s [H/128,I/128]) is
     asked once for every FFN expert the sample routes to, so a layer with hundreds of experts costs the oracle
-    only the experts (and rows) of the sample.  shared as in moe_layer_fp32.  Returns fp32 [n, H]."""
+    only the experts (and rows) of the sample.  shared as in moe_layer_fp32.  Returns fp32 [n, H]; with
+    return_magnitude also the sum of the ABSOLUTE values of the terms each output element is the sum of (weighted expert
+    rows, identity term, shared expert's row): what the roundings of stored intermediate values scale with."""
     idx = _i32(idx)
     w = np.ascontiguousarray(w, dtype=np.float32)
     n, k = idx.shape
     xq, xs = quant_1x128(x_bits, div_mode=1)
     H = xq.shape[1]
     out = np.zeros((n, H), dtype=np.float32)
+    mag = np.zeros((n, H), dtype=np.float32)
     for e in np.unique(idx[idx >= 0]):
         tt, jj = np.nonzero(idx == e)
         gu_q, gu_s, d_q, d_s = expert_weights(int(e))
         ex = np.array([0, len(tt)], dtype=np.int32)
         gu = grouped_gemm_fp8(xq[tt], xs[tt], gu_q[None], gu_s[None], ex)
         aq, a_s = quant_1x128_f32(swiglu(gu))
-        y = grouped_gemm_fp8(aq, a_s, d_q[None], d_s[None], ex)
-        np.add.at(out, tt, y * w[tt, jj][:, None])
+        y = grouped_gemm_fp8(aq, a_s, d_q[None], d_s[None], ex) * w[tt, jj][:, None]
+        np.add.at(out, tt, y)
+        np.add.at(mag, tt, np.abs(y))
     zs = np.where(idx < 0, w, 0).sum(1).astype(np.float32)
-    out += bf16_to_f32(x_bits) * zs[:, None]
+    ident = bf16_to_f32(x_bits) * zs[:, None]
+    out += ident
+    mag += np.abs(ident)
     if shared is not None:
         sgu_q, sgu_s, sd_q, sd_s = shared
         ex1 = np.array([0, n], dtype=np.int32)
         sg = grouped_gemm_fp8(xq, xs, sgu_q, sgu_s, ex1)
         sa_q, sa_s = quant_1x128_f32(swiglu(sg))
-        out += grouped_gemm_fp8(sa_q, sa_s, sd_q, sd_s, ex1)
-    return out
+        sh = grouped_gemm_fp8(sa_q, sa_s, sd_q, sd_s, ex1)
+        out += sh
+        mag += np.abs(sh)
+    return (out, mag) if return_magnitude else out
