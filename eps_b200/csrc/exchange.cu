@@ -292,29 +292,28 @@ put_kernel(Peers peers, PutArgs a) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kXWarps + (threadIdx.x >> 5);
   const int64_t n_warps = (int64_t)gridDim.x * kXWarps;
-  const int n = a.W * a.S;
-  const int n_sent = a.T > 0 ? a.send_incl[n - 1] : 0;
   const int hvecs = (int)(a.hidden_row_bytes >> 4);
-  // Every rank starts with the rows for its right-hand neighbour and walks the send order cyclically from there: at any
-  // moment the ranks of the box store to DIFFERENT destinations.  (In plain send order all ranks would store to
-  // rank 0 first, then to rank 1, ...: one GPU's ingress at a time carries the whole exchange.)
-  const int first_dest = (a.rank + 1) % a.W;
-  const int64_t shift = first_dest == 0 ? 0 : a.send_incl[first_dest * a.S - 1];
-  for (int64_t i0 = warp; i0 < n_sent; i0 += n_warps) {
-    const int64_t i = i0 + shift < n_sent ? i0 + shift : i0 + shift - n_sent;
-    // window j = (dest, stage) of row i: the first j with i < send_incl[j]
-    int j = 0;
-    for (int j0 = 0; j0 < n; j0 += 32) {
-      const int jj = j0 + lane;
-      const bool mine = jj < n && i < a.send_incl[jj];
-      const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (m != 0) {
-        j = j0 + __ffs(m) - 1;
-        break;
-      }
-    }
-    const int dest = j / a.S, s = j % a.S;
-    if (a.stage >= 0 && s != a.stage) continue;
+  // Rows are taken round-robin over the DESTINATIONS (unit u -> destination (u + rank) % W, its (u / W)-th row), so a
+  // rank stores to all of its peers at once and every peer's ingress carries one W-th of every sender's stream at any
+  // moment, however far the ranks have drifted apart.  (In plain send order all ranks would store to rank 0 first, then
+  // to rank 1, ...: one GPU's ingress at a time carries the whole exchange.)
+  int64_t longest = 0;   // rows of the largest destination block
+  for (int d = 0; d < a.W; d++) {
+    const int jb = d * a.S + (a.stage < 0 ? 0 : a.stage), je = d * a.S + (a.stage < 0 ? a.S - 1 : a.stage);
+    const int64_t lo = jb == 0 ? 0 : a.send_incl[jb - 1], hi = a.send_incl[je];
+    longest = hi - lo > longest ? hi - lo : longest;
+  }
+  if (a.T <= 0) longest = 0;
+  for (int64_t u = warp; u < longest * a.W; u += n_warps) {
+    const int dest_u = (int)((u + a.rank) % a.W);
+    const int jb = dest_u * a.S + (a.stage < 0 ? 0 : a.stage), je = dest_u * a.S + (a.stage < 0 ? a.S - 1 : a.stage);
+    const int64_t lo = jb == 0 ? 0 : a.send_incl[jb - 1], hi = a.send_incl[je];
+    const int64_t i = lo + u / a.W;
+    if (i >= hi) continue;
+    // window j = (dest, stage) of row i: the first j in [jb, je] with i < send_incl[j]
+    int j = jb;
+    while (j < je && i >= a.send_incl[j]) j++;
+    const int dest = dest_u;
     const int64_t begin = j == 0 ? 0 : a.send_incl[j - 1];
     const int64_t r = (int64_t)a.disp_off[j] + (i - begin);
     const int t = a.send_map[i] % a.T;
@@ -371,16 +370,21 @@ local_reduce_put_kernel(Peers peers, const uint8_t* __restrict__ y, const int32_
   const int64_t row_bytes = H * 2;
   const int64_t sentinel = (int64_t)ret_incl[W * S - 1] * k;
   const int s0 = stage < 0 ? 0 : stage, s1 = stage < 0 ? S : stage + 1;
-  int64_t seen = 0;
-  // destinations in cyclic order from the right-hand neighbour on: the ranks of the box store to different peers at
-  // any moment instead of all to rank 0, then all to rank 1, ...
-  for (int dd = 0; dd < W; dd++) {
-    const int d = (rank + 1 + dd) % W;
+  // rows round-robin over the destinations, like put_kernel: unit u -> destination (u + rank) % W, its (u / W)-th row
+  int64_t longest = 0;
+  for (int d = 0; d < W; d++) {
     const int jb = d * S + s0, je = d * S + s1 - 1;
     const int64_t b = jb == 0 ? 0 : ret_incl[jb - 1], e = ret_incl[je];
-    uint8_t* dst_base = peers.base[d] + off_out + (int64_t)comb_off[jb] * row_bytes;
-    const int64_t first = (warp - seen % n_warps + n_warps) % n_warps;
-    for (int64_t q = b + first; q < e; q += n_warps) {
+    longest = e - b > longest ? e - b : longest;
+  }
+  {
+    for (int64_t u = warp; u < longest * W; u += n_warps) {   // (the extra brace keeps the loop body's indentation)
+      const int d = (int)((u + rank) % W);
+      const int jb = d * S + s0, je = d * S + s1 - 1;
+      const int64_t b = jb == 0 ? 0 : ret_incl[jb - 1], e = ret_incl[je];
+      const int64_t q = b + u / W;
+      if (q >= e) continue;
+      uint8_t* dst_base = peers.base[d] + off_out + (int64_t)comb_off[jb] * row_bytes;
       int32_t rows[kSlots];
 #pragma unroll
       for (int j = 0; j < kSlots; j++) {
@@ -408,7 +412,6 @@ local_reduce_put_kernel(Peers peers, const uint8_t* __restrict__ y, const int32_
         st_16(dst + (int64_t)v * 16, o);
       }
     }
-    seen += e - b;
   }
   signal_when_grid_done(peers, off_flags, flag_slot, W, rank, epoch, cta_counter);
 }
