@@ -423,8 +423,10 @@ def main():
     gemm_ms = statistics.mean(a.elapsed_time(b) for a, b in gemm_events) if gemm_events else None
     ctx = layer.sched.context
     excl = ctx.excl.cpu().numpy()
-    D = int(excl[-1])
     EL = cfg.num_experts // world
+    # the timed launch is the FIRST stage's gate/up GEMM: its experts are the first EL / stages of the rank
+    excl = excl[:EL // stages + 1]
+    D = int(excl[-1])
     live = int(((excl[1:] - excl[:-1]) > 0).sum())
     I = cfg.inter
     w_bytes = live * (2 * I * H + (2 * I // 128) * (H // 128) * 4)
