@@ -98,7 +98,8 @@ class Communicator:
             local = ctypes.c_void_p(0)
         peers = [local.value] * self.world
         if self.world > 1:
-            dev = torch.device("cuda", torch.cuda.current_device())
+            on_gpu = dist.get_backend(self.group) == "nccl"    # the handles travel on the group's own device type
+            dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
             allh = torch.empty((self.world, 64), dtype=torch.uint8, device=dev)
             ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=dev)

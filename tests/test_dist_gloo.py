@@ -107,6 +107,74 @@ def test_exchange_over_gloo(world, S, E, k, T):
         assert msg == "ok", f"rank {rank}: {msg}"
 
 
+def _symm_worker(rank, world, port, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from eps_b200 import _lib
+        from eps_b200.communication import Communicator, CommunicatorParams, SymmetricMemoryUnavailable
+
+        comm = Communicator(None, CommunicatorParams(rank, world, world), transport="ipc")
+        real = _lib.call
+        opened, freed = [], []
+
+        def fake(name, *args):
+            # rank 0 allocates and opens fine; rank 1 cannot open its peer's handle (the failure is made on the host)
+            if name == "epsb_symm_alloc":
+                args[1]._obj.value = 0x1000 * (rank + 1)
+                return 0
+            if name == "epsb_symm_open":
+                if rank == 1:
+                    raise _lib.EpsError("epsb_symm_open: peer access is not available (code 2)")
+                args[1]._obj.value = 0x9000
+                opened.append(0x9000)
+                return 0
+            if name == "epsb_symm_close":
+                opened.remove(args[0])
+                return 0
+            if name == "epsb_symm_free":
+                freed.append(args[0])
+                return 0
+            return real(name, *args)
+
+        _lib.call = fake
+        try:
+            comm.symm_alloc(4096)
+            q.put((rank, "symm_alloc did not raise"))
+            return
+        except SymmetricMemoryUnavailable:
+            pass          # on BOTH ranks, although only rank 1 failed
+        finally:
+            _lib.call = real
+        assert opened == [] and freed == [0x1000 * (rank + 1)], (opened, freed)
+        assert comm._regions == []
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+def test_symmetric_memory_failure_is_collective():
+    """One rank cannot map its peer's region: every rank releases what it holds and raises the same exception (the
+    caller's fall-back to the other transport is then the same decision on all ranks).  The failure is injected on the
+    host; no GPU is involved."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + 911) % 2000
+    procs = [ctx.Process(target=_symm_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
 def test_single_rank_never_touches_a_process_group():
     from eps_b200.communication import Communicator, CommunicatorParams
 
