@@ -22,6 +22,7 @@ CASES = [
     (1, 1, 128, 8, 2100, 0, 8192),
     (1, 1, 256, 8, 4096, 0, 4096),      # benchmark size on one rank
     (8, 2, 256, 8, 1024, 0, 4096),      # 8 ranks, 32 experts each, 2 stages
+    (8, 1, 256, 8, 4096, 0, 4096),      # benchmark size on eight ranks: every rank receives ~21 600 tokens
     (4, 1, 768, 12, 300, 256, 512),     # 512 FFN + 256 identity experts would be E=512; here E=768 FFN stresses the bucket count
 ]
 
