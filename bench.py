@@ -70,6 +70,29 @@ def host_cores() -> int:
         return os.cpu_count() or 1
 
 
+def bind_to_gpu_numa_node(device_index: int):
+    """One process per GPU: keep this process (and so the pinned host buffers it allocates next) on the CPUs of the NUMA
+    node the GPU hangs off, as a deployment would.  Only narrows the affinity when the host reports such a node and it is
+    a proper subset of the CPUs the process may use; returns what it did for the JSON line, or None."""
+    try:
+        p = torch.cuda.get_device_properties(device_index)
+        path = f"/sys/bus/pci/devices/{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0/local_cpulist"
+        cpus = set()
+        for part in open(path).read().strip().split(","):
+            if not part:
+                continue
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        local = cpus & allowed
+        if len(local) < 2 or local == allowed:
+            return None
+        os.sched_setaffinity(0, local)
+        return {"cpus": len(local), "of": len(allowed)}
+    except Exception:   # no sysfs node information, no permission: run unbound
+        return None
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -237,6 +260,8 @@ def main():
     ap.add_argument("--stages", type=int, default=None, help="EPS stages (default 1)")
     ap.add_argument("--graph", action="store_true",
                     help="diagnostics (N=1): also time the resident step replayed as one CUDA graph (key cuda_graph)")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="N > 1: do not bind the rank to the CPUs of its GPU's NUMA node before allocating pinned buffers")
     ap.add_argument("--shared-late", action="store_true",
                     help="diagnostics: run the shared expert after the routed experts instead of under the dispatch")
     ap.add_argument("--min-seconds", type=float, default=2.0,
@@ -271,6 +296,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    host_binding = bind_to_gpu_numa_node(local_rank) if (world > 1 and not args.no_numa_bind) else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -514,6 +540,8 @@ def main():
         }
         if graph_info is not None:
             line["cuda_graph"] = graph_info
+        if world > 1:
+            line["host_binding"] = host_binding if host_binding is not None else "unbound"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
